@@ -23,7 +23,8 @@ def register_cache_kind(kind: str, first_needed: Callable[["CacheNeed", int], in
 @dataclass(frozen=True)
 class CacheNeed:
     """Keys and values per position: `kind` says which positions must be kept ("full": all;
-    "window": the last `window`; or a registered kind of the mixer's own)."""
+    "window": the last `window`; "chunk": the chunk of `window` positions the next query lies in; or a registered kind
+    of the mixer's own)."""
     kind: str
     kv_heads: int
     head_dim: int
@@ -37,8 +38,8 @@ class CacheNeed:
     def __post_init__(self):
         if self.kind not in CACHE_KINDS:
             raise ValueError(f"cache kind {self.kind!r}; known: {', '.join(sorted(CACHE_KINDS))}")
-        if (self.kind == "window") != (self.window is not None) and self.kind in ("full", "window"):
-            raise ValueError("a window cache needs a window, a full cache has none")
+        if (self.kind in ("window", "chunk")) != (self.window is not None) and self.kind in ("full", "window", "chunk"):
+            raise ValueError("a window or chunk cache needs its size, a full cache has none")
 
     def first_needed(self, length: int) -> int:
         return CACHE_KINDS[self.kind](self, length)
@@ -46,6 +47,8 @@ class CacheNeed:
 
 register_cache_kind("full", lambda need, length: 0)
 register_cache_kind("window", lambda need, length: length - need.window + 1)
+# chunks of `window` positions counted from 0: a later query sees nothing before the start of the chunk `length` lies in
+register_cache_kind("chunk", lambda need, length: length - length % need.window)
 
 
 @dataclass(frozen=True)

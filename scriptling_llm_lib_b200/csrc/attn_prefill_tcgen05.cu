@@ -77,7 +77,7 @@ __device__ __forceinline__ bool ft_item(const FtArgs& p, int round, FtItem& it) 
   it.g = it.h / (p.H / p.G);
   int q_lo = it.pos0 + it.r0;
   it.q_hi = it.pos0 + it.r0 + it.nq - 1;
-  int k_first = p.window > 0 ? max(0, q_lo - p.window + 1) : 0;
+  int k_first = first_seen(q_lo, p.window);
   it.t_lo = k_first / FT_BK;
   it.t_hi = it.q_hi / FT_BK;
   it.n_tiles = it.t_hi - it.t_lo + 1;
@@ -258,7 +258,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int round = 0; ok && ft_item(p, round, it); round++) {
     if (!it.valid) continue;
     const int n_tiles = it.n_tiles, t_lo = it.t_lo, t_hi = it.t_hi, q_hi = it.q_hi, nq = it.nq, row0 = it.row0, r0 = it.r0, h = it.h;
-    const int qpos = it.pos0 + r0 + r;
+    const int qpos = it.pos0 + r0 + r, qfirst = first_seen(qpos, p.window);
     float m_ref = -INFINITY, l = 0.f;              // reference maximum (raw score units) and sum relative to it
     for (int j = 0; j < n_tiles && ok; j++) {
       const int Jg = J0 + j;
@@ -271,13 +271,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tmem_ld32(t_lane + a * 64 + 32, s1);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       // ---- mask, row maximum (raw scores; four independent chains)
-      bool need_mask = (t * FT_BK + FT_BK - 1 > qpos) || (p.window > 0 && t * FT_BK <= qpos - p.window);
+      bool need_mask = (t * FT_BK + FT_BK - 1 > qpos) || t * FT_BK < qfirst;
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 32; i++) {
           int k0 = t * FT_BK + i, k1 = k0 + 32;
-          if (!(k0 <= qpos && (p.window == 0 || k0 > qpos - p.window))) s0[i] = 0xff800000u;   // -inf
-          if (!(k1 <= qpos && (p.window == 0 || k1 > qpos - p.window))) s1[i] = 0xff800000u;
+          if (!(k0 <= qpos && k0 >= qfirst)) s0[i] = 0xff800000u;   // -inf
+          if (!(k1 <= qpos && k1 >= qfirst)) s1[i] = 0xff800000u;
         }
       }
       float mxa = ft_max3(__uint_as_float(s0[0]), __uint_as_float(s0[1]), __uint_as_float(s0[2]));
@@ -418,7 +418,7 @@ __device__ __forceinline__ void fp_tile(const FtArgs& p, FpTile& s, int h, int q
   s.nq = min(FT_BQ, S - s.r0);
   int q_lo = pos0 + s.r0;
   s.q_hi = pos0 + s.r0 + s.nq - 1;
-  int k_first = p.window > 0 ? max(0, q_lo - p.window + 1) : 0;
+  int k_first = first_seen(q_lo, p.window);
   s.t_lo = k_first / FT_BK;
   s.t_hi = s.q_hi / FT_BK;
   s.n_tiles = s.t_hi - s.t_lo + 1;
@@ -472,13 +472,13 @@ __device__ __forceinline__ float ft_rowmax(const uint32_t (&s)[64]) {
   return fmaxf(ft_max3(m[0], m[1], m[2]), m[3]);
 }
 // scores of keys the query at qpos does not see become -inf (tile t holds keys 64 t ... 64 t + 63)
-__device__ __forceinline__ void ft_mask(uint32_t (&s)[64], int t, int qpos, int window) {
-  bool need = (t * FT_BK + FT_BK - 1 > qpos) || (window > 0 && t * FT_BK <= qpos - window);
+__device__ __forceinline__ void ft_mask(uint32_t (&s)[64], int t, int qpos, int qfirst) {
+  bool need = (t * FT_BK + FT_BK - 1 > qpos) || t * FT_BK < qfirst;
   if (need) {
 #pragma unroll
     for (int i = 0; i < 64; i++) {
       int k = t * FT_BK + i;
-      if (!(k <= qpos && (window == 0 || k > qpos - window))) s[i] = 0xff800000u;   // -inf
+      if (!(k <= qpos && k >= qfirst)) s[i] = 0xff800000u;   // -inf
     }
   }
 }
@@ -657,7 +657,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int n_union = it.n_union, T_lo = it.T_lo;
     if (sb.valid) {
     const int n_tiles = sb.n_tiles, t_lo = sb.t_lo, seq_end = it.seq_end;
-    const int qpos = it.pos0 + sb.r0 + r;
+    const int qpos = it.pos0 + sb.r0 + r, qfirst = first_seen(qpos, p.window);
     float m_ref = -INFINITY, l = 0.f;              // reference maximum (raw score units) and sum relative to it
     uint32_t s[64];
     float mx;
@@ -675,7 +675,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         __syncwarp();
         if (lane == 0) mbar_arrive(b_sempty + 8 * bf);
       }
-      ft_mask(s, t, qpos, p.window);
+      ft_mask(s, t, qpos, qfirst);
       mx = ft_rowmax(s);
       // ---- move the reference maximum only when the row's maximum has outgrown it by 2^8
       bool grow = mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * sc > 8.0f);

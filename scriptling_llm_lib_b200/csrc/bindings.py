@@ -237,6 +237,14 @@ class KernelSet:
         return self._mix
 
     @property
+    def gate(self) -> "GateKernels":
+        """The kernels around gated mixers and side inputs (whole-projection query/key norm with the cache write,
+        a gate per head, a norm on the way into the stream, a cap on the logits), for this set's element type."""
+        if getattr(self, "_gate", None) is None:
+            self._gate = GateKernels(self.dtype)
+        return self._gate
+
+    @property
     def decode(self) -> "DecodeKernels":
         if self.dtype != torch.bfloat16:
             raise KernelError("the decode kernels are bfloat16 only")
@@ -868,21 +876,35 @@ class MixKernels:
             _ptr(ctx.slots, torch.int32, "slots"), self._view(out, "out"), c_int(out.stride(0)), c_int(ctx.n_seqs),
             c_int(max(1, ctx.max_new)), c_int(inner), c_int(n_state), _stream()), "selective_scan")
 
-    def moe_route(self, z, correction, idx, wgt, n_groups, keep, top, scale):
-        """z float32 [T, E] the router's logits -> idx int32 [T, top] the chosen experts, wgt float32 [T, top] their weights."""
+    def moe_route(self, z, correction, idx, wgt, n_groups, keep, top, scale, top_softmax=False):
+        """z float32 [T, E] the router's logits -> idx int32 [T, top] the chosen experts, wgt float32 [T, top] their weights.
+        `top_softmax`: the highest z + correction (a bias; may be None) are chosen and weigh with the softmax over the
+        chosen ones alone; else sigmoid scores, a correction that only enters the picking, runs of experts."""
         T, E = z.shape
         _check(self._fn("moe_route")(_ptr(z, torch.float32, "z"), _ptr(correction, torch.float32, "correction"), c_int(1),
                                      _ptr(idx, torch.int32, "idx"), _ptr(wgt, torch.float32, "wgt"), c_int(T), c_int(E),
-                                     c_int(n_groups), c_int(keep), c_int(top), c_float(scale), _stream()), "moe_route")
+                                     c_int(n_groups), c_int(keep), c_int(top), c_float(scale), c_int(1 if top_softmax else 0),
+                                     _stream()), "moe_route")
 
-    def moe_pairs(self, h, wup, wdown, idx, wgt, hid, out):
-        """wup [E, F, K], wdown [E, N, F]; out float32 [top, T, N] partial sums over a token's chosen experts."""
+    def moe_pairs(self, h, wup, wdown, idx, wgt, hid, out, glu=None):
+        """wup [E, F, K], wdown [E, N, F]; out float32 [top, T, N] partial sums over a token's chosen experts.
+        `glu` = (limit, alpha): wup is [E, 2 F, K] (gate rows, then up rows) and the clamped gate is the activation."""
         T, K = h.shape
         top = idx.shape[1]
+        F = wdown.shape[2]
         _check(self._fn("moe_pairs")(self._view(h, "h"), c_int(h.stride(0)), _ptr(wup, self.dtype, "wup"),
                                      _ptr(wdown, self.dtype, "wdown"), _ptr(idx, torch.int32, "idx"), _ptr(wgt, torch.float32, "wgt"),
                                      _ptr(hid, self.dtype, "hid"), _ptr(out, torch.float32, "out"), c_int(T), c_int(top), c_int(K),
-                                     c_int(wup.shape[1]), c_int(wdown.shape[1]), _stream()), "moe_pairs")
+                                     c_int(F), c_int(wdown.shape[1]), c_int(0 if glu is None else 1),
+                                     c_float(0.0 if glu is None else glu[0]), c_float(0.0 if glu is None else glu[1]), _stream()),
+               "moe_pairs")
+
+    def glu_clamp(self, gu, out, limit, alpha, rows_used=None):
+        """out [rows, F] = the clamped gate of gu [rows, 2 F] (F gate sums, then F up sums a row): g' * sigmoid(alpha g') *
+        (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit). `rows_used`: an int32 on the device, rows from there on stay."""
+        _check(self._fn("glu_clamp")(_ptr(gu, self.dtype, "gu"), _ptr(out, self.dtype, "out"), c_int(out.shape[0]),
+                                     c_int(out.shape[1]), c_float(limit), c_float(alpha), _ptr(rows_used, torch.int32, "rows_used"),
+                                     _stream()), "glu_clamp")
 
     def moe_group_rows(self, idx, counts, offsets, pair_of_row, row_of_pair=None, tile_group=None, pad=1):
         """Groups the (token, expert) pairs of idx [T, top] by expert. counts int32 [E] must be zero and is left
@@ -897,16 +919,18 @@ class MixKernels:
                                           _stream()), "moe_group_rows")
         LAUNCHES[0] += 4
 
-    def moe_grouped(self, h, wup, wdown, wgt, offsets, pair_of_row, hid, out):
+    def moe_grouped(self, h, wup, wdown, wgt, offsets, pair_of_row, hid, out, glu=None, raw=None):
         """The experts' products over rows grouped without padding (`moe_group_rows` with pad 1), float32 sums on
-        the FMA units; out float32 [top, T, N]."""
+        the FMA units; out float32 [top, T, N]. `glu` = (limit, alpha) with `raw` [T * top, 2 F] scratch: gated experts."""
         T, K = h.shape
         top = wgt.shape[1]
         _check(self._fn("moe_grouped")(self._view(h, "h"), c_int(h.stride(0)), _ptr(wup, self.dtype, "wup"),
                                        _ptr(wdown, self.dtype, "wdown"), _ptr(wgt, torch.float32, "wgt"),
                                        _ptr(offsets, torch.int32, "offsets"), _ptr(pair_of_row, torch.int32, "pair_of_row"),
                                        _ptr(hid, self.dtype, "hid"), _ptr(out, torch.float32, "out"), c_int(T), c_int(top),
-                                       c_int(wup.shape[0]), c_int(K), c_int(wup.shape[1]), c_int(wdown.shape[1]), _stream()),
+                                       c_int(wup.shape[0]), c_int(K), c_int(wdown.shape[2]), c_int(wdown.shape[1]),
+                                       c_int(0 if glu is None else 1), c_float(0.0 if glu is None else glu[0]),
+                                       c_float(0.0 if glu is None else glu[1]), _ptr(raw, self.dtype, "raw"), _stream()),
                "moe_grouped")
         LAUNCHES[0] += 1
 
@@ -922,6 +946,76 @@ class MixKernels:
         _check(self._fn("moe_combine")(_ptr(ys, torch.float32, "ys"), _ptr(row_of_pair, torch.int32, "row_of_pair"),
                                        _ptr(wgt, torch.float32, "wgt"), _ptr(out, torch.float32, "out"), c_int(T), c_int(top),
                                        c_int(out.shape[1]), _stream()), "moe_combine")
+
+
+class GateKernels:
+    """Launchers of gate_kernels.cuh. `dtype` is the element type of activations and weights; norms, gates,
+    angles and the residual sum are float32 in both sets."""
+
+    def __init__(self, dtype: torch.dtype):
+        if dtype not in _SUFFIX:
+            raise KernelError(f"no kernels for {dtype}; supported: float32, bfloat16")
+        self.dtype, self.suffix = dtype, _SUFFIX[dtype]
+        self.lib = load_library("gate_" + self.suffix)
+        self._fns: dict[str, object] = {}
+
+    _fn = SequenceKernels._fn
+    _flag = SequenceKernels._flag
+    _view = staticmethod(SequenceKernels._view)
+
+    def qk_norm_store(self, c, q_out, tok_pos, tok_seq, block_table, cos_sin, kpages, vpages, n_heads, n_kv, head_dim, v_dim,
+                      rot, interleaved, q_weight, k_weight, eps):
+        """Row t of c (float32 or element type; a view) holds [queries | keys | values] of a token. Queries and keys are
+        each divided by the root mean square of their whole part and multiplied by q_weight / k_weight (None: as
+        they are), turned by the table over their first `rot` dims, and go to q_out [T, n_heads * head_dim] and, with
+        the values, to the rows' places in the cache pages (n_kv == 0: queries only)."""
+        w_f32 = 0
+        for w in (q_weight, k_weight):
+            if w is not None:
+                w_f32 = self._flag(w, "norm weight")
+        _check(self._fn("qk_norm_store")(
+            self._view(c, "c"), c_int(self._flag(c, "c")), c_int(c.stride(0)), self._view(q_out, "q_out"), c_int(q_out.stride(0)),
+            _ptr(tok_pos, torch.int32, "tok_pos"), _ptr(tok_seq, torch.int32, "tok_seq"),
+            _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1] if block_table is not None else 0),
+            _ptr(cos_sin, torch.float32, "cos_sin"), _ptr(kpages, self.dtype if kpages is not None else None, "kpages"),
+            _ptr(vpages, self.dtype if vpages is not None else None, "vpages"), c_int(c.shape[0]), c_int(n_heads), c_int(n_kv),
+            c_int(head_dim), c_int(v_dim), c_int(rot), c_int(1 if interleaved else 0), _ptr(q_weight, None, "q_weight"),
+            _ptr(k_weight, None, "k_weight"), c_int(w_f32), c_float(eps), _stream()), "qk_norm_store")
+
+    def head_gate(self, o, g, n_heads, v_dim):
+        """o [T, n_heads * v_dim] (element type) *= sigmoid(g [T, n_heads]) per head; g a view, float32 or element type."""
+        _check(self._fn("head_gate")(self._view(o, "o"), c_int(o.stride(0)), self._view(g, "g"), c_int(self._flag(g, "g")),
+                                     c_int(g.stride(0)), c_int(o.shape[0]), c_int(n_heads), c_int(v_dim), _stream()), "head_gate")
+
+    def add_cast(self, x, delta, xb):
+        """x float32 [T, d] += delta (None, [T, d] float32 or element type, or float32 [P, T, d] partial sums);
+        xb [T, d] = x in the element type."""
+        P = 0 if delta is None else (delta.shape[0] if delta.dim() == 3 else 1)
+        if delta is not None and (tuple(delta.shape[-2:]) != tuple(x.shape) or not delta.is_contiguous()):
+            raise KernelError(f"addend {tuple(delta.shape)} does not fit the stream {tuple(x.shape)}")
+        _check(self._fn("add_cast")(_ptr(x, torch.float32, "x"), _ptr(delta, None, "delta"),
+                                    c_int(self._flag(delta, "delta") if delta is not None else 0), c_int(P),
+                                    _ptr(xb, self.dtype, "xb"), ctypes.c_longlong(x.numel()), _stream()), "add_cast")
+
+    def gelu_mul_rows(self, a, ids, table, col0, out):
+        """out [T, D] = gelu_tanh(a [T, D]) * table[ids[t], col0 : col0 + D]."""
+        _check(self._fn("gelu_mul_rows")(self._view(a, "a"), c_int(a.stride(0)), _ptr(ids, torch.int32, "ids"),
+                                         _ptr(table, self.dtype, "table"), c_int(table.shape[1]), c_int(col0),
+                                         _ptr(out, self.dtype, "out"), c_int(a.shape[0]), c_int(a.shape[1]), _stream()),
+               "gelu_mul_rows")
+
+    def add_rms_normed(self, x, y, weight, eps):
+        """x float32 [T, d] += y / sqrt(mean(y^2) + eps) * weight; y [T, d] or [P, T, d] partial sums (float32 or element type)."""
+        P = y.shape[0] if y.dim() == 3 else 1
+        if tuple(y.shape[-2:]) != tuple(x.shape):
+            raise KernelError(f"y {tuple(y.shape)} does not fit the stream {tuple(x.shape)}")
+        _check(self._fn("add_rms_normed")(_ptr(x, torch.float32, "x"), _ptr(y, None, "y"), c_int(self._flag(y, "y")), c_int(P),
+                                          c_int(x.shape[0]), _ptr(weight, None, "weight"), c_int(self._flag(weight, "weight")),
+                                          c_int(x.shape[1]), c_float(eps), _stream()), "add_rms_normed")
+
+    def softcap(self, x, cap):
+        """x float32 = cap * tanh(x / cap), in place."""
+        _check(self._fn("softcap")(_ptr(x, torch.float32, "x"), ctypes.c_longlong(x.numel()), c_float(cap), _stream()), "softcap")
 
 
 class CastKernels:

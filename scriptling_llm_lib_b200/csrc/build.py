@@ -38,6 +38,8 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...]]] = {
     "seq_bf16": ("lib_seq_bf16.cu", ("common.cuh", "sequence_kernels.cuh", "sequence_launchers.inc")),
     "mix_f32": ("lib_mix_f32.cu", ("common.cuh", "mix_kernels.cuh", "mix_launchers.inc")),
     "mix_bf16": ("lib_mix_bf16.cu", ("common.cuh", "mix_kernels.cuh", "mix_launchers.inc")),
+    "gate_f32": ("lib_gate_f32.cu", ("common.cuh", "gate_kernels.cuh", "gate_launchers.inc")),
+    "gate_bf16": ("lib_gate_bf16.cu", ("common.cuh", "gate_kernels.cuh", "gate_launchers.inc")),
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

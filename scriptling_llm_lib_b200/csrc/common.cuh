@@ -19,6 +19,16 @@ SLLM_EXPORT int sllm_page_tokens(void) { return SLLM_PAGE; }
 
 typedef __nv_bfloat16 bf16;
 
+// Which of the keys at or before its own position a query sees, as the one number every attention
+// kernel takes under the name `window`: 0 all of them; w > 0 the last w (a sliding window); w < 0
+// those of its own chunk of -w positions, chunks counted from position 0 of the sequence. The
+// first seen position never falls as the query's position grows, so a tile of queries starts at
+// the first position its first query sees.
+__host__ __device__ __forceinline__ int first_seen(int qpos, int window) {
+  if (window > 0) return qpos - window + 1 > 0 ? qpos - window + 1 : 0;
+  return window < 0 ? qpos - qpos % (-window) : 0;
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
 template <typename T> __device__ __forceinline__ T from_f32(float v);

@@ -499,7 +499,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32, NREP == 1 ? 7 : 1) attn_decode_
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int slot = lane / LPK, dl = (lane % LPK) * 8;
   int pos = p.seq_pos0[b];
-  int k_begin = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  int k_begin = first_seen(pos, p.window);
   int pb = k_begin / SLLM_PAGE, pe = pos / SLLM_PAGE;
   int pps = (pe - pb + 1 + p.n_split - 1) / p.n_split;
   int p0 = pb + split * pps, p1 = min(pe + 1, p0 + pps);
@@ -742,7 +742,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_mma_kernel(AttnDeco
   const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = lane >> 2, t = lane & 3;
   const int pos = p.seq_pos0[b];
-  const int k_begin = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int k_begin = first_seen(pos, p.window);
   const int pb = k_begin / SLLM_PAGE, pe = pos / SLLM_PAGE;
   const int pps = (pe - pb + 1 + p.n_split - 1) / p.n_split;
   const int p0 = pb + split * pps, p1 = min(pe + 1, p0 + pps);

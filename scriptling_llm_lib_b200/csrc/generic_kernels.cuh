@@ -551,7 +551,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_paged_kernel(AttnArgs p) {
   }
 
   int k_hi = pos0 + r0 + nq;                                   // one past the last key any query sees
-  int k_lo = p.window > 0 ? max(0, pos0 + r0 - p.window + 1) : 0;
+  int k_lo = first_seen(pos0 + r0, p.window);
   k_lo = (k_lo / ATT_BK) * ATT_BK;
   const int* bt = p.block_table + (size_t)b * p.max_pages;
 
@@ -577,7 +577,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_paged_kernel(AttnArgs p) {
       float dot = 0.f;
       for (int dd = 0; dd < hd; dd++) dot = fmaf(qv[dd], kv[dd], dot);
       float s = dot * p.scale;
-      bool seen = page >= 0 && kpos <= qpos && (p.window == 0 || kpos > qpos - p.window);
+      bool seen = page >= 0 && kpos <= qpos && kpos >= first_seen(qpos, p.window);
       if (!seen) s = -INFINITY;
       float m_new = fmaxf(m[i], warp_max(s));
       if (m_new == -INFINITY) continue;                        // nothing seen yet by this query
@@ -663,7 +663,7 @@ __global__ void __launch_bounds__(256) attn_paged_tiled_kernel(AttnArgs p) {
       for (int c = 0; c < 4; c++) o[i][gg][c] = 0.f;
   }
   const int k_hi = pos0 + r0 + nq;
-  int k_lo = p.window > 0 ? max(0, pos0 + r0 - p.window + 1) : 0;
+  int k_lo = first_seen(pos0 + r0, p.window);
   k_lo = (k_lo / ATT2_BK) * ATT2_BK;
   const int* bt = p.block_table + (size_t)b * p.max_pages;
 
@@ -707,7 +707,7 @@ __global__ void __launch_bounds__(256) attn_paged_tiled_kernel(AttnArgs p) {
 #pragma unroll
       for (int j = 0; j < 4; j++) {
         int kpos = kt + tx * 4 + j;
-        bool seen = page >= 0 && qi < nq && kpos <= qpos && (p.window == 0 || kpos > qpos - p.window);
+        bool seen = page >= 0 && qi < nq && kpos <= qpos && kpos >= first_seen(qpos, p.window);
         s[i][j] = seen ? s[i][j] * p.scale : -INFINITY;
         mx = fmaxf(mx, s[i][j]);
       }
@@ -808,7 +808,7 @@ __global__ void __launch_bounds__(128) attn_decode_split_generic_kernel(AttnSpli
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = lane / LPK, dl = (lane % LPK) * 4;
   const int pos = p.seq_pos0[b];
-  const int k_begin = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const int k_begin = first_seen(pos, p.window);
   const int pb = k_begin / SLLM_PAGE, pe = pos / SLLM_PAGE;
   const int pps = (pe - pb + p.n_split) / p.n_split;
   const int p0 = pb + split * pps, p1 = min(pe + 1, p0 + pps);

@@ -911,7 +911,9 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
 }
 
 // ------------------------------------------------------------------ routed experts
-// router: a warp per token. z [T][E] float32 are the router's logits (a product of the library, float32 sums);
+// router: a warp per token. z [T][E] float32 are the router's logits (a product of the library, float32 sums).
+// mode 1: c = z + bias (corr; may be null), the `top` experts with the highest c are picked and count with the
+// softmax over the picked c alone (n_groups 1, scale unused). mode 0:
 // s = sigmoid(z), c = s + correction. The experts are cut into n_groups runs of equal length, a run is rated by its best
 // two c added up, the `keep` best-rated runs stay open, and among the open experts the `top` with the highest c are picked
 // (ties: the lower index). Expert e then counts with s_e / (sum of the picked s + 1e-20) * scale.
@@ -920,7 +922,7 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
 __global__ void __launch_bounds__(32 * MIX_ROUTE_WARPS) moe_route_kernel(const float* __restrict__ z, const void* __restrict__ corr,
                                                                          int corr_f32, int* __restrict__ idx,
                                                                          float* __restrict__ wgt, int T, int E, int n_groups,
-                                                                         int keep, int top, float scale) {
+                                                                         int keep, int top, float scale, int mode) {
   extern __shared__ __align__(16) float sm[];
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   int t = blockIdx.x * MIX_ROUTE_WARPS + wid;
@@ -929,9 +931,10 @@ __global__ void __launch_bounds__(32 * MIX_ROUTE_WARPS) moe_route_kernel(const f
   float* ch = s + E;                                  // [E] the picking scores c (-inf once picked or in a run that is shut)
   float* gs = ch + E;                                 // [n_groups]
   for (int e = lane; e < E; e += 32) {
-    float sg = sigmoid_f(z[(size_t)t * E + e]);
+    float zz = z[(size_t)t * E + e];
+    float sg = mode ? zz + (corr ? load_w(corr, corr_f32, e) : 0.f) : sigmoid_f(zz);
     s[e] = sg;
-    ch[e] = sg + load_w(corr, corr_f32, e);
+    ch[e] = mode ? sg : sg + load_w(corr, corr_f32, e);
   }
   __syncwarp();
   int gsz = E / n_groups;
@@ -966,7 +969,7 @@ __global__ void __launch_bounds__(32 * MIX_ROUTE_WARPS) moe_route_kernel(const f
     }
   }
   __syncwarp();
-  float sum = 0.f;
+  float sum = 0.f, first = 0.f;
   for (int k = 0; k < top; k++) {
     float best = -INFINITY;
     int bi = -1;
@@ -980,7 +983,8 @@ __global__ void __launch_bounds__(32 * MIX_ROUTE_WARPS) moe_route_kernel(const f
       if (oi >= 0 && (bi < 0 || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
     }
     if (bi < 0) bi = 0;                           // fewer experts allowed than asked for: cannot happen with a checked configuration
-    float sv = s[bi];
+    if (k == 0) first = s[bi];                    // the largest picked logit: the softmax's reference (mode 1)
+    float sv = mode ? expf(s[bi] - first) : s[bi];
     sum += sv;
     if (lane == 0) {
       idx[(size_t)t * top + k] = bi;
@@ -989,12 +993,31 @@ __global__ void __launch_bounds__(32 * MIX_ROUTE_WARPS) moe_route_kernel(const f
     }
     __syncwarp();
   }
-  float f = scale / (sum + 1e-20f);
+  float f = mode ? 1.0f / sum : scale / (sum + 1e-20f);
   for (int k = lane; k < top; k += 32) wgt[(size_t)t * top + k] *= f;
+}
+
+// The clamped gate of an expert: g' * sigmoid(alpha * g') * (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+__device__ __forceinline__ float glu_clamp_f(float g, float u, float limit, float alpha) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * sigmoid_f(alpha * g) * (u + 1.0f);
+}
+// gu [rows][2 F]: F gate sums then F up sums a row; out[row][f] = the clamped gate of (gu[row][f], gu[row][F + f]).
+// Rows from *rows_used on (when given) are left alone.
+template <typename A>
+__global__ void glu_clamp_kernel(const A* __restrict__ gu, A* __restrict__ out, int rows, int F, float limit, float alpha,
+                                 const int* __restrict__ rows_used) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * F) return;
+  int r = (int)(i / F), f = (int)(i % F);
+  if (rows_used && r >= *rows_used) return;
+  out[i] = from_f32<A>(glu_clamp_f(to_f32(gu[(size_t)r * 2 * F + f]), to_f32(gu[(size_t)r * 2 * F + F + f]), limit, alpha));
 }
 
 // Few rows (a decode step): every (token, chosen expert) pair on its own, a warp per output column.
 //   up:   hid[p][f] = relu(Wup[e_p][f] . h[t_p])^2           p = t * top + k
+//         gated (Wup holds F gate rows, then F up rows, per expert): hid[p][f] = glu(Wup[e_p][f] . h, Wup[e_p][F + f] . h)
 //   down: out[k][t][j] = wgt[p] * (Wdown[e_p][j] . hid[p])    float32 partial sums over k, added by the reader
 template <typename A>
 __device__ __forceinline__ float warp_dot(const A* __restrict__ x, const A* __restrict__ w, int K, int lane, int vec) {
@@ -1015,12 +1038,20 @@ __device__ __forceinline__ float warp_dot(const A* __restrict__ x, const A* __re
 template <typename A>
 __global__ void __launch_bounds__(128) moe_pair_up_kernel(const A* __restrict__ h, int ldh, const A* __restrict__ wup,
                                                           const int* __restrict__ idx, A* __restrict__ hid, int top, int K, int F,
-                                                          int vec) {
+                                                          int vec, int gated, float limit, float alpha) {
   int p = blockIdx.y;
   int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
   int f = blockIdx.x * nw + wid;
   if (f >= F) return;
-  float a = warp_dot(h + (size_t)(p / top) * ldh, wup + ((size_t)idx[p] * F + f) * K, K, lane, vec);
+  const A* x = h + (size_t)(p / top) * ldh;
+  if (gated) {
+    const A* we = wup + (size_t)idx[p] * 2 * F * K;
+    float g = warp_dot(x, we + (size_t)f * K, K, lane, vec);
+    float u = warp_dot(x, we + (size_t)(F + f) * K, K, lane, vec);
+    if (lane == 0) hid[(size_t)p * F + f] = from_f32<A>(glu_clamp_f(g, u, limit, alpha));
+    return;
+  }
+  float a = warp_dot(x, wup + ((size_t)idx[p] * F + f) * K, K, lane, vec);
   if (lane == 0) hid[(size_t)p * F + f] = from_f32<A>(a > 0.f ? a * a : 0.f);
 }
 
@@ -1104,6 +1135,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ ys, const int* __re
 // through shared memory, 4 x 4 outputs a thread, float32 sums. Tile `blockIdx.x` of the rows: the experts' row
 // ranges are cut into tiles of 64 in order; a block beyond the last tile leaves.
 //   mode 0 (up):   a row's input is h[pair / top]; out: hid[row][col] = relu(acc)^2 (element type)
+//   mode 2 (up):   the same input; out: hid[row][col] = acc (element type), for an activation that pairs columns
 //   mode 1 (down): a row's input is hid[row]; out[pair % top][pair / top][col] = wgt[pair] * acc (float32)
 template <typename A>
 __global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(const A* __restrict__ in, int ldin, const A* __restrict__ w,
@@ -1131,7 +1163,7 @@ __global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(const A* __restri
   int col0 = blockIdx.y * 64;
   if (threadIdx.x < 64) {
     int r = threadIdx.x;
-    src_row[r] = r < n_rows ? (mode == 0 ? pair_of_row[r0 + r] / top : r0 + r) : -1;
+    src_row[r] = r < n_rows ? (mode != 1 ? pair_of_row[r0 + r] / top : r0 + r) : -1;
   }
   __syncthreads();
   const A* wexp = w + (size_t)e * N * K;
@@ -1168,12 +1200,12 @@ __global__ void __launch_bounds__(256) moe_grouped_gemm_kernel(const A* __restri
   for (int a = 0; a < 4; a++) {
     int r = ty * 4 + a;
     if (r >= n_rows) continue;
-    if (mode == 0) {
+    if (mode != 1) {
       A* orow = (A*)out + (size_t)(r0 + r) * N;
 #pragma unroll
       for (int c = 0; c < 4; c++) {
         int col = col0 + tx * 4 + c;
-        if (col < N) orow[col] = from_f32<A>(acc[a][c] > 0.f ? acc[a][c] * acc[a][c] : 0.f);
+        if (col < N) orow[col] = from_f32<A>(mode == 2 ? acc[a][c] : acc[a][c] > 0.f ? acc[a][c] * acc[a][c] : 0.f);
       }
     } else {
       int pr = pair_of_row[r0 + r];

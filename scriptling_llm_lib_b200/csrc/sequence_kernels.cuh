@@ -299,7 +299,7 @@ __global__ void __launch_bounds__(128) attn_wide_value_kernel(const A* __restric
     for (int j = threadIdx.x; j < hd; j += 128) qs[j] = to_f32(q[(size_t)t * q_ld + (size_t)h * hd + j]) * scale;
     __syncthreads();
   }
-  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  int lo = first_seen(pos, window);
   float m = -INFINITY, l = 0.f, acc[NV];
 #pragma unroll
   for (int i = 0; i < NV; i++) acc[i] = 0.f;

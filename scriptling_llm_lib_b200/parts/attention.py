@@ -13,6 +13,17 @@ before it is cached. Either sends the step's keys and values through a store ker
 rotation, value norm and cache write in one pass (`kv_store`); values as wide as keys then still
 use the attention kernels below, other widths a kernel that takes both (`attn_wide_value`).
 
+Four more options, none in the reference. `chunk`: a query sees the earlier keys of its own chunk of that many
+positions only, chunks counted from position 0 of the sequence (not from where a step begins); the cache
+gives pages back once the chunk they belong to has passed. `conv`: a short causal convolution over time on
+every channel of the projected queries, keys and values, straight behind the projection; the last taps - 1
+projected rows of a sequence are its state. `qk_norm`: queries and keys are each divided by the root mean
+square of the WHOLE projection (all heads at once) and multiplied by a weight of that size, before the
+rotation. `gate_name`: a matrix [n_heads, hidden] on the mixer's own input; head h's output is multiplied by
+the sigmoid of its logit before the output product. With `conv` or `qk_norm` the step's rows go through one
+kernel that norms, rotates and fills the cache (`qk_norm_store`), in float32 from the convolution's float32
+output; the attention kernels are the same ones.
+
 The position encoding is optional (`position=None`: queries and keys as projected). Storing keys
 and values in the cache is this mixer's own step, whatever the encoding: for an encoding that is a
 rotation by a table the store and the rotation are one kernel (or part of the q|k|v product's
@@ -27,7 +38,10 @@ import torch
 
 from ..cache.needs import CacheNeed
 from ..csrc.bindings import DecodeKernels, PrefillAttentionTC
+from ..cache.needs import StateNeed
+from ..weights.spec import TensorSpec
 from .base import MIXERS, POSITION_ENCODINGS, Folded, Mixer, PartSpec
+from .conv import CausalConv
 from .linear import Linear
 
 
@@ -40,12 +54,20 @@ class Attention(Mixer):
 
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PartSpec | None,
                  q_name: str, k_name: str, v_name: str, o_name: str, window: int | None = None,
-                 scale: float | None = None, v_dim: int | None = None, value_norm_eps: float | None = None):
+                 scale: float | None = None, v_dim: int | None = None, value_norm_eps: float | None = None,
+                 chunk: int | None = None, conv: dict | None = None, qk_norm: dict | None = None, gate_name: str | None = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} key/value heads")
         if not 1 <= head_dim <= 512:
             raise ValueError(f"head_dim {head_dim}: the attention kernels take head widths 1..512")
+        if window and chunk:
+            raise ValueError("an attention layer has a sliding window or chunks, not both")
+        if chunk is not None and chunk < 1:
+            raise ValueError(f"chunks of {chunk} positions")
         self.hidden, self.n_heads, self.n_kv_heads, self.head_dim, self.window = hidden, n_heads, n_kv_heads, head_dim, window
+        self.chunk = int(chunk) if chunk else None
+        # what the kernels take as `window`: > 0 a sliding window, < 0 chunks of that many positions, 0 every earlier key
+        self.span = int(window) if window else (-self.chunk if self.chunk else 0)
         self.v_dim = head_dim if v_dim is None else int(v_dim)
         self.value_norm_eps = None if value_norm_eps is None else float(value_norm_eps)
         if self.v_dim < 1 or self.v_dim > 512:
@@ -53,17 +75,47 @@ class Attention(Mixer):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.position = POSITION_ENCODINGS.build(position) if position is not None else None
         qw, kw = n_heads * head_dim, n_kv_heads * head_dim
-        self.qkv = Linear([q_name, k_name, v_name], [qw, kw, n_kv_heads * self.v_dim], hidden)
+        vw = n_kv_heads * self.v_dim
+        self.gate_name = gate_name
+        names, widths = [q_name, k_name, v_name], [qw, kw, vw]
+        if gate_name is not None:               # the gates' logits ride in the same product, behind the values
+            names, widths = names + [gate_name], widths + [n_heads]
+        self.qkv = Linear(names, widths, hidden)
         self.out = Linear([o_name], [hidden], n_heads * self.v_dim)
         self.q_only: Linear | None = None
+        self.conv = None
+        if conv is not None and int(conv["taps"]) > 1:
+            self.conv = CausalConv([conv["q_name"], conv["k_name"], conv["v_name"]], [qw, kw, vw], int(conv["taps"]))
+        self.qk_norm = dict(qk_norm) if qk_norm is not None else None
+        self.q_norm_w = self.k_norm_w = None
+
+    @property
+    def prepared(self) -> bool:
+        """The step's rows pass the convolution and / or the whole-projection norm on their way into the cache."""
+        return self.conv is not None or self.qk_norm is not None
 
     def tensor_specs(self):
-        return self.qkv.tensor_specs() + self.out.tensor_specs()
+        specs = self.qkv.tensor_specs() + self.out.tensor_specs()
+        if self.conv is not None:
+            specs += self.conv.tensor_specs()
+        if self.qk_norm is not None:
+            specs += [TensorSpec(self.qk_norm["q_name"], (self.n_heads * self.head_dim,), init="norm_weight"),
+                      TensorSpec(self.qk_norm["k_name"], (self.n_kv_heads * self.head_dim,), init="norm_weight")]
+        return specs
 
     def bind(self, tensors, dtype, device):
         self.qkv.bind(tensors, dtype, device)
         self.out.bind(tensors, dtype, device)
         self.q_only = self.qkv.rows(0, self.n_heads * self.head_dim)
+        if self.conv is not None:
+            self.conv.bind(tensors, dtype, device)
+        if self.qk_norm is not None:
+            self.q_norm_w = tensors[self.qk_norm["q_name"]].float().contiguous()
+            self.k_norm_w = tensors[self.qk_norm["k_name"]].float().contiguous()
+
+    def state_need(self):
+        need = self.conv.state_need() if self.conv is not None else None
+        return {"conv": need} if need is not None else None
 
     def prepare(self, max_positions, device):
         if self.position is not None:
@@ -85,7 +137,8 @@ class Attention(Mixer):
                                   self.head_dim, rot, interleaved)
 
     def cache_need(self):
-        return CacheNeed("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window,
+        kind = "window" if self.window else "chunk" if self.chunk else "full"
+        return CacheNeed(kind, self.n_kv_heads, self.head_dim, self.window or self.chunk,
                          v_dim=None if self.v_dim == self.head_dim else self.v_dim)
 
     @property
@@ -102,6 +155,8 @@ class Attention(Mixer):
     def takes_folded(self, ctx, rows: int) -> bool:
         """The q|k|v product can scale its own output rows: in a decode step of few rows, and in a long
         prompt step (the tensor-core product, with or without the rotation in its epilogue)."""
+        if self.prepared or self.gate_name is not None:
+            return False
         path = self.qkv.fold_path(ctx, rows, ctx.dtype)
         return path is not None and self.q_only.fold_path(ctx, rows, ctx.dtype) == path and (ctx.is_decode or path == "tiles")
 
@@ -110,12 +165,78 @@ class Attention(Mixer):
         path = self.out.fold_path(ctx, rows, ctx.dtype, finishing=True)
         return path is not None and (ctx.is_decode or path == "tiles")
 
-    def forward(self, x, ctx, unit, writes, fold=None):
+    def _attend(self, qkv, x, ctx, kpages, vpages, block_table, fast_decode, fusion, writes):
+        """The step's queries (the leading columns of `qkv`) over the cache -> [T, n_heads * v_dim]."""
+        attn = torch.empty((x.shape[0], self.n_heads * self.v_dim), dtype=x.dtype, device=x.device)
+        if self.other_widths:
+            ctx.kernels.seq.attn_wide_value(qkv, attn, ctx.tok_pos, ctx.tok_seq, block_table, kpages, vpages, self.n_heads,
+                                            self.n_kv_heads, self.head_dim, self.v_dim, self.span, self.scale)
+        elif fast_decode:
+            n_split = ctx.decode_splits(self.n_heads, self.n_kv_heads, self.head_dim)
+            scratch = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
+                                  device=x.device)
+            tickets = ctx.engine.tickets(ctx.n_seqs * self.n_kv_heads)
+            if fusion is not None:      # rotation and cache write happen inside the attention kernel
+                ctx.kernels.decode.attn_decode_rope(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, scratch, tickets,
+                                                    fusion[0], fusion[1], fusion[2], writes, ctx.n_seqs, self.n_heads,
+                                                    self.n_kv_heads, self.head_dim, self.span, self.scale, n_split)
+            else:
+                ctx.kernels.decode.attn_decode(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, scratch, ctx.n_seqs,
+                                               self.n_heads, self.n_kv_heads, self.head_dim, self.span, self.scale,
+                                               n_split, tickets=tickets)
+        elif x.dtype == torch.bfloat16 and self.head_dim in PrefillAttentionTC.HEAD_DIMS:
+            ctx.kernels.prefill_attention_tc.attn(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages,
+                                                  ctx.n_seqs, ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim,
+                                                  self.span, self.scale, ctx.err_flag)
+        elif ctx.is_decode and ctx.kernels.attn_decode_split_takes(self.head_dim, qkv.stride(0)):
+            # one query per sequence on the generic path (the whole 32-bit decode step): keys split over blocks
+            n_split = ctx.kernels.attn_decode_splits(ctx.n_seqs, self.n_heads, self.n_kv_heads, ctx.max_pages, ctx.engine.sm_count)
+            part = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
+                               device=x.device) if n_split > 1 else None
+            ctx.kernels.attn_decode_split(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, part, ctx.n_seqs,
+                                          self.n_heads, self.n_kv_heads, self.head_dim, self.span, self.scale, n_split)
+        else:
+            ctx.kernels.attn_paged(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages, ctx.n_seqs,
+                                   ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim, self.span, self.scale)
+        return attn
+
+    def _forward_prepared(self, x, ctx, writes, state, kpages, vpages, block_table, fold):
+        """The path of a layer with a convolution, a whole-projection norm or a gate: one product for queries, keys,
+        values and gate logits; convolution (float32 out); norm, rotation and cache write in one kernel; attention;
+        gate; output product."""
+        if not writes:
+            raise ValueError("a layer with a convolution, a query/key norm or a gate fills its own cache unit")
+        T = x.shape[0]
+        qw, kw, vw = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim, self.n_kv_heads * self.v_dim
+        y = self.qkv.forward(x, ctx)
+        c = y[:, :qw + kw + vw]
+        if self.conv is not None:
+            c = self.conv.forward(c, state["conv"], ctx, torch.float32)
+        rotation = self.position.rotation() if self.position is not None else None
+        if self.position is not None and rotation is None:
+            raise ValueError("a layer with a convolution or a query/key norm takes a position encoding that is a rotation")
+        table, rot, interleaved = rotation if rotation is not None else (None, 0, False)
+        q = torch.empty((T, qw), dtype=x.dtype, device=x.device)
+        eps = float(self.qk_norm["eps"]) if self.qk_norm is not None else 0.0
+        ctx.kernels.gate.qk_norm_store(c, q, ctx.tok_pos, ctx.tok_seq, block_table, table, kpages, vpages, self.n_heads,
+                                       self.n_kv_heads, self.head_dim, self.v_dim, rot, interleaved, self.q_norm_w, self.k_norm_w, eps)
+        fast_decode = (ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in DecodeKernels.HEAD_DIMS
+                       and not self.other_widths)
+        attn = self._attend(q, x, ctx, kpages, vpages, block_table, fast_decode, None, writes)
+        if self.gate_name is not None:
+            ctx.kernels.gate.head_gate(attn, y[:, qw + kw + vw:], self.n_heads, self.v_dim)
+        if fold is not None:
+            return self.out.forward_folded(attn, ctx, fold=fold)
+        return self.out.forward(attn, ctx, partials_ok=True)
+
+    def forward(self, x, ctx, unit, writes, fold=None, state=None):
         if isinstance(x, Folded):
             folded, x = x, x.x
         else:
             folded = None
         kpages, vpages, block_table = ctx.unit_kv(unit)
+        if self.prepared or self.gate_name is not None:
+            return self._forward_prepared(x, ctx, writes, state, kpages, vpages, block_table, fold)
         fast_decode = ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in DecodeKernels.HEAD_DIMS
         rotation = self.position.rotation() if self.position is not None else None
         tc = ctx.kernels.tensor_core if x.dtype == torch.bfloat16 else None
@@ -140,37 +261,7 @@ class Attention(Mixer):
             if fusion is None:
                 self._store(qkv, ctx, rotation, self.n_kv_heads if writes else 0, kpages if writes else None,
                             vpages if writes else None, block_table)
-        attn = torch.empty((x.shape[0], self.n_heads * self.v_dim), dtype=x.dtype, device=x.device)
-        if self.other_widths:
-            ctx.kernels.seq.attn_wide_value(qkv, attn, ctx.tok_pos, ctx.tok_seq, block_table, kpages, vpages, self.n_heads,
-                                            self.n_kv_heads, self.head_dim, self.v_dim, self.window, self.scale)
-        elif fast_decode:
-            n_split = ctx.decode_splits(self.n_heads, self.n_kv_heads, self.head_dim)
-            scratch = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
-                                  device=x.device)
-            tickets = ctx.engine.tickets(ctx.n_seqs * self.n_kv_heads)
-            if fusion is not None:      # rotation and cache write happen inside the attention kernel
-                ctx.kernels.decode.attn_decode_rope(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, scratch, tickets,
-                                                    fusion[0], fusion[1], fusion[2], writes, ctx.n_seqs, self.n_heads,
-                                                    self.n_kv_heads, self.head_dim, self.window, self.scale, n_split)
-            else:
-                ctx.kernels.decode.attn_decode(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, scratch, ctx.n_seqs,
-                                               self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale,
-                                               n_split, tickets=tickets)
-        elif x.dtype == torch.bfloat16 and self.head_dim in PrefillAttentionTC.HEAD_DIMS:
-            ctx.kernels.prefill_attention_tc.attn(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages,
-                                                  ctx.n_seqs, ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim,
-                                                  self.window, self.scale, ctx.err_flag)
-        elif ctx.is_decode and ctx.kernels.attn_decode_split_takes(self.head_dim, qkv.stride(0)):
-            # one query per sequence on the generic path (the whole 32-bit decode step): keys split over blocks
-            n_split = ctx.kernels.attn_decode_splits(ctx.n_seqs, self.n_heads, self.n_kv_heads, ctx.max_pages, ctx.engine.sm_count)
-            part = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
-                               device=x.device) if n_split > 1 else None
-            ctx.kernels.attn_decode_split(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, part, ctx.n_seqs,
-                                          self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale, n_split)
-        else:
-            ctx.kernels.attn_paged(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages, ctx.n_seqs,
-                                   ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.scale)
+        attn = self._attend(qkv, x, ctx, kpages, vpages, block_table, fast_decode, fusion, writes)
         if fold is not None:
             return self.out.forward_folded(attn, ctx, fold=fold)
         return self.out.forward(attn, ctx, partials_ok=True)

@@ -28,6 +28,8 @@ Interfaces (duck-typed; the base classes document them):
                                               += delta when rows is None; rows picks rows to norm;
                                               delta: None or either form of y
   PositionEncoding.prepare(max_positions, device); .rotation() or .transform(...)   see below
+  StreamInput.forward(residual, delta, ctx)   reads the stream itself (after taking the pending addend in) and
+                                              the step's token ids, and adds to the stream in place
 
 A norm between two products can be folded into them (optional, and only where all three agree): a
 row's 1/rms is one number, so (v / rms * w) W^T = (1 / rms) * ((v * w) W^T). A norm that can be
@@ -145,6 +147,15 @@ class PositionEncoding(Part):
         raise NotImplementedError
 
 
+class StreamInput(Part):
+    """A part that is no sublayer on a norm's output: it reads the residual stream as it stands (the pending
+    addend `delta` taken in first) together with what the step knows of its tokens (`ctx.token_ids`), and adds
+    its result to the stream in place. Nothing is left pending behind it."""
+
+    def forward(self, residual, delta, ctx) -> None:
+        raise NotImplementedError
+
+
 class Embedding(Part):
     def forward(self, ids, ctx):
         raise NotImplementedError
@@ -182,5 +193,6 @@ FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 ARRANGEMENTS = Registry("block arrangement")
+STREAM_INPUTS = Registry("stream input")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("output head")

@@ -30,7 +30,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Mapping
 
-from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, FoldRequest, PartSpec
+from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, STREAM_INPUTS, FoldRequest, PartSpec
 
 
 @dataclass(frozen=True)
@@ -236,7 +236,55 @@ class SandwichNormBlock(Block):
         return NormedAddend(self.feed_forward.forward(h2, ctx), self.feed_forward_post_norm)
 
 
+class PreNormInputBlock(Block):
+    """x += mixer(norm(x)); then, where the layer has a feed-forward, x += feed_forward(norm(x)); then, where it has
+    one, a stream input: a part that reads the stream as it stands and the step's tokens and adds to it. Roles:
+    `mixer_norm`, `mixer`, both or neither of `feed_forward_norm`, `feed_forward`, and optionally `stream_input`.
+    The mixer may keep per-sequence state (it is handed the unit's as `state=`); the norms are of the kind that
+    takes a plain pending addend (`rmsnorm`)."""
+
+    def __init__(self, spec: LayerSpec):
+        self.mixer_norm = NORMS.build(_role(spec, "mixer_norm"))
+        self.mixer = MIXERS.build(_role(spec, "mixer"))
+        has = [r in spec.parts for r in ("feed_forward_norm", "feed_forward")]
+        if has[0] != has[1]:
+            raise ValueError("a layer has a feed-forward and its norm, or neither")
+        self.feed_forward_norm = NORMS.build(spec.parts["feed_forward_norm"]) if has[0] else None
+        self.feed_forward = FEED_FORWARDS.build(spec.parts["feed_forward"]) if has[1] else None
+        self.stream_input = STREAM_INPUTS.build(spec.parts["stream_input"]) if "stream_input" in spec.parts else None
+
+    def parts(self):
+        out = [self.mixer_norm, self.mixer]
+        if self.feed_forward is not None:
+            out += [self.feed_forward_norm, self.feed_forward]
+        if self.stream_input is not None:
+            out.append(self.stream_input)
+        return out
+
+    @staticmethod
+    def _addend(y, ctx):
+        """A sublayer's output in a form the norms take: float32 sums of a 16-bit engine travel as one partial sum."""
+        import torch
+        if isinstance(y, torch.Tensor) and y.dim() == 2 and y.dtype == torch.float32 and ctx.dtype != torch.float32:
+            return y.unsqueeze(0)
+        return y
+
+    def forward(self, residual, delta, ctx, unit, writes):
+        st = ctx.unit_state(unit) if self.state_need() is not None else None
+        h = self.mixer_norm.forward(residual, delta, ctx)
+        a = self.mixer.forward(h, ctx, unit, writes, state=st) if st is not None else self.mixer.forward(h, ctx, unit, writes)
+        a = self._addend(a, ctx)
+        if self.feed_forward is not None:
+            h2 = self.feed_forward_norm.forward(residual, a, ctx)
+            a = self._addend(self.feed_forward.forward(h2, ctx), ctx)
+        if self.stream_input is None:
+            return a
+        self.stream_input.forward(residual, a, ctx)
+        return None
+
+
 ARRANGEMENTS.register("pre_norm", PreNormBlock)
+ARRANGEMENTS.register("pre_norm_input", PreNormInputBlock)
 ARRANGEMENTS.register("sandwich_norm", SandwichNormBlock)
 ARRANGEMENTS.register("scaled_pre_norm", ScaledPreNormBlock)
 

@@ -40,10 +40,14 @@ class TokenEmbedding(Embedding):
 
 class OutputHead(Head):
     """Logits in float32 for the rows it is given. `tied`: the matrix is another part's tensor (the
-    embedding's), named by `weight_name`, and is not asked of the weight file a second time."""
+    embedding's), named by `weight_name`, and is not asked of the weight file a second time. `softcap` (absent in the
+    reference): the logits leave as cap * tanh(logits / cap)."""
 
-    def __init__(self, vocab: int, width: int, weight_name: str, tied: bool = False):
+    def __init__(self, vocab: int, width: int, weight_name: str, tied: bool = False, softcap: float | None = None):
         self.vocab, self.width, self.tied = vocab, width, tied
+        self.softcap = float(softcap) if softcap else None
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"a cap on the logits must be positive, got {softcap}")
         self.linear = Linear([weight_name], [vocab], width)
 
     def tensor_specs(self):
@@ -56,7 +60,10 @@ class OutputHead(Head):
         self.linear.bind(tensors, dtype, device)
 
     def forward(self, normed, ctx):
-        return self.linear.forward(normed, ctx, out_dtype=torch.float32)
+        logits = self.linear.forward(normed, ctx, out_dtype=torch.float32)
+        if self.softcap is not None:
+            ctx.kernels.gate.softcap(logits, self.softcap)
+        return logits
 
 
 EMBEDDINGS.register("token_embedding", TokenEmbedding)
@@ -67,5 +74,8 @@ def token_embedding(vocab: int, width: int, name: str) -> PartSpec:
     return PartSpec("token_embedding", dict(vocab=vocab, width=width, name=name))
 
 
-def linear_head(vocab: int, width: int, weight_name: str, tied: bool = False) -> PartSpec:
-    return PartSpec("linear_head", dict(vocab=vocab, width=width, weight_name=weight_name, tied=tied))
+def linear_head(vocab: int, width: int, weight_name: str, tied: bool = False, softcap: float | None = None) -> PartSpec:
+    params = dict(vocab=vocab, width=width, weight_name=weight_name, tied=tied)
+    if softcap:
+        params["softcap"] = softcap
+    return PartSpec("linear_head", params)

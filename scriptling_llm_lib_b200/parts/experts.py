@@ -13,6 +13,12 @@ c inside an open run still beats it). Among the open experts the `top` with the 
 and expert e counts with s_e / (sum of the picked s + 1e-20) * scale. The output is the sum of the
 picked experts' outputs with those factors.
 
+Two more choices. `router="top_softmax"`: z = Wr x + bias (the stored vector is a bias on the logits here), the
+`top` experts with the largest z are picked, and they count with the softmax over the picked logits alone (no
+runs, no scale). `act="clamped_glu"`: an expert has a gate and an up matrix; with g = min(Wg x, limit) and
+u = clamp(Wu x, -limit, limit) its inner vector is g * sigmoid(alpha g) * (u + 1), alpha = 1.702 unless
+given. Gate and up rows are stacked per expert ([experts, 2 ff, hidden]) and multiplied in one pass.
+
 The experts' matrices are stacked [experts, ff, hidden] and [experts, hidden, ff]. A step of few
 rows runs every (token, chosen expert) pair by itself (each streams its expert's matrices once); a
 longer step groups the pairs by expert on the device and runs tiles of rows per expert: in bfloat16
@@ -31,6 +37,7 @@ from .base import FEED_FORWARDS, FeedForward
 from .linear import Linear
 
 ACTS = ("gelu_tanh", "relu_squared", "silu")
+ROUTERS = ("grouped_sigmoid", "top_softmax")
 
 
 class ActFeedForward(FeedForward):
@@ -69,11 +76,26 @@ class RoutedExperts(FeedForward):
     PAIRS_ONE_BY_ONE = 64        # up to this many (token, expert) pairs in a step each pair runs by itself
 
     def __init__(self, hidden: int, intermediate: int, experts: int, top: int, n_groups: int, keep_groups: int, scale: float,
-                 router_name: str, correction_name: str, up_names: list, down_names: list, act: str = "relu_squared"):
-        if act != "relu_squared":
-            raise ValueError("the experts' kernels apply the square of relu")
+                 router_name: str, correction_name: str | None, up_names: list, down_names: list, act: str = "relu_squared",
+                 router: str = "grouped_sigmoid", gate_names: list | None = None, limit: float | None = None,
+                 alpha: float = 1.702):
+        if act not in ("relu_squared", "clamped_glu"):
+            raise ValueError("the experts' kernels apply the square of relu or the clamped gate (clamped_glu)")
+        if router not in ROUTERS:
+            raise ValueError(f"router {router!r}; known: {', '.join(ROUTERS)}")
         if len(up_names) != experts or len(down_names) != experts:
             raise ValueError(f"{experts} experts need as many up and down matrices")
+        self.glu = None
+        if act == "clamped_glu":
+            if gate_names is None or len(gate_names) != experts or limit is None or not float(limit) > 0:
+                raise ValueError("gated experts need a gate matrix each and a positive limit")
+            self.glu = (float(limit), float(alpha))
+        self.gate_names = list(gate_names) if self.glu is not None else None
+        self.top_softmax = router == "top_softmax"
+        if self.top_softmax and n_groups != 1:
+            raise ValueError("the top_softmax router knows no runs of experts")
+        if not self.top_softmax and correction_name is None:
+            raise ValueError("the grouped_sigmoid router needs its correction")
         if n_groups < 1 or experts % n_groups or not 1 <= keep_groups <= n_groups:
             raise ValueError(f"{experts} experts cannot form {n_groups} equal groups of which {keep_groups} are kept")
         if not 1 <= top <= keep_groups * (experts // n_groups):
@@ -85,19 +107,26 @@ class RoutedExperts(FeedForward):
         self.up_names, self.down_names = list(up_names), list(down_names)
 
     def tensor_specs(self):
-        specs = self.router.tensor_specs() + [TensorSpec(self.correction_name, (self.E,), init="bias")]
-        for u, d in zip(self.up_names, self.down_names):
+        specs = self.router.tensor_specs()
+        if self.correction_name is not None:
+            specs.append(TensorSpec(self.correction_name, (self.E,), init="bias"))
+        for j, (u, d) in enumerate(zip(self.up_names, self.down_names)):
+            if self.glu is not None:
+                specs.append(TensorSpec(self.gate_names[j], (self.F, self.hidden)))
             specs += [TensorSpec(u, (self.F, self.hidden)), TensorSpec(d, (self.hidden, self.F))]
         return specs
 
     def elements_read_per_step(self) -> int:
         """A decode step reads the router and, per token, `top` experts: counted once (one token)."""
-        return self.E * self.hidden + self.E + self.top * 2 * self.F * self.hidden
+        return self.E * self.hidden + self.E + self.top * (3 if self.glu is not None else 2) * self.F * self.hidden
 
     def bind(self, tensors, dtype, device):
         self.router.bind(tensors, dtype, device)
-        self.correction = tensors[self.correction_name].float().contiguous()
-        self.w_up = torch.stack([tensors[n] for n in self.up_names]).contiguous()        # [E, F, hidden]
+        self.correction = tensors[self.correction_name].float().contiguous() if self.correction_name is not None else None
+        if self.glu is not None:                                                         # [E, 2 F, hidden]: gate rows, up rows
+            self.w_up = torch.stack([torch.cat([tensors[g], tensors[u]]) for g, u in zip(self.gate_names, self.up_names)]).contiguous()
+        else:
+            self.w_up = torch.stack([tensors[n] for n in self.up_names]).contiguous()    # [E, F, hidden]
         self.w_down = torch.stack([tensors[n] for n in self.down_names]).contiguous()    # [E, hidden, F]
         self.counts = torch.zeros((self.E,), dtype=torch.int32, device=device)
         if self.w_up.dtype != dtype:
@@ -115,11 +144,11 @@ class RoutedExperts(FeedForward):
         idx = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         wgt = torch.empty((T, self.top), dtype=torch.float32, device=dev)
         z = self.router.forward(x, ctx, out_dtype=torch.float32)                  # logits, float32 sums
-        k.moe_route(z, self.correction, idx, wgt, self.n_groups, self.keep, self.top, self.scale)
+        k.moe_route(z, self.correction, idx, wgt, self.n_groups, self.keep, self.top, self.scale, top_softmax=self.top_softmax)
         if pairs <= self.PAIRS_ONE_BY_ONE:
             hid = torch.empty((pairs, self.F), dtype=x.dtype, device=dev)
             out = torch.empty((self.top, T, self.hidden), dtype=torch.float32, device=dev)
-            k.moe_pairs(x, self.w_up, self.w_down, idx, wgt, hid, out)
+            k.moe_pairs(x, self.w_up, self.w_down, idx, wgt, hid, out, glu=self.glu)
             return out
         offsets = torch.empty((self.E + 1,), dtype=torch.int32, device=dev)
         if not self._on_tensor_cores(x):
@@ -127,7 +156,8 @@ class RoutedExperts(FeedForward):
             k.moe_group_rows(idx, self.counts, offsets, pair_of_row)
             hid = torch.empty((pairs, self.F), dtype=x.dtype, device=dev)
             out = torch.empty((self.top, T, self.hidden), dtype=torch.float32, device=dev)
-            k.moe_grouped(x, self.w_up, self.w_down, wgt, offsets, pair_of_row, hid, out)
+            raw = torch.empty((pairs, 2 * self.F), dtype=x.dtype, device=dev) if self.glu is not None else None
+            k.moe_grouped(x, self.w_up, self.w_down, wgt, offsets, pair_of_row, hid, out, glu=self.glu, raw=raw)
             return out
         # every expert's rows from a multiple of 128 on, so that a tile of the tensor-core product has one expert
         tile = 128
@@ -140,7 +170,12 @@ class RoutedExperts(FeedForward):
         k.moe_gather_rows(x, pair_of_row, self.top, xs)
         tc = ctx.kernels.tensor_core
         hid = torch.empty((rows, self.F), dtype=x.dtype, device=dev)
-        tc.gemm_grouped(xs, self.w_up, hid, tile_group, ctx.err_flag, act="relu_squared", rows_used=offsets[self.E:])
+        if self.glu is not None:
+            raw = torch.empty((rows, 2 * self.F), dtype=x.dtype, device=dev)
+            tc.gemm_grouped(xs, self.w_up, raw, tile_group, ctx.err_flag, rows_used=offsets[self.E:])
+            k.glu_clamp(raw, hid, self.glu[0], self.glu[1], rows_used=offsets[self.E:])
+        else:
+            tc.gemm_grouped(xs, self.w_up, hid, tile_group, ctx.err_flag, act="relu_squared", rows_used=offsets[self.E:])
         ys = torch.empty((rows, self.hidden), dtype=torch.float32, device=dev)
         tc.gemm_grouped(hid, self.w_down, ys, tile_group, ctx.err_flag, rows_used=offsets[self.E:])
         out = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)

@@ -1,0 +1,65 @@
+"""A per-layer input from the token itself, gated by the residual stream.
+
+Every token has a second, narrow embedding e (a row of a table shared by all layers, of which layer i reads
+the columns [i * dim, (i + 1) * dim)). With x the residual stream as it stands behind the layer's sublayers:
+
+    g = gelu_tanh(Wgate x) * e        [dim]
+    y = Wproj g                       [width]
+    x += y / sqrt(mean(y^2) + eps) * w
+
+The stream's sum and the norm are float32; the two products are the library's (in the engine's dtype on the
+stream rounded once, with float32 sums), the second one leaving float32. The table is one tensor for the
+model: the first layer that asks for it owns it in the weight list, the others name it as theirs (`owns_table`).
+Not in the reference.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..weights.spec import TensorSpec
+from .base import STREAM_INPUTS, StreamInput
+from .linear import Linear
+
+
+class TokenSideInput(StreamInput):
+    graph_safe = True
+
+    def __init__(self, width: int, dim: int, vocab: int, table_name: str, table_width: int, column: int, gate_name: str,
+                 proj_name: str, norm_name: str, eps: float, owns_table: bool = True):
+        if dim < 1 or column < 0 or column + dim > table_width:
+            raise ValueError(f"columns {column}..{column + dim} are outside a table of width {table_width}")
+        self.width, self.dim, self.vocab, self.eps = width, dim, vocab, float(eps)
+        self.table_name, self.table_width, self.column, self.owns_table = table_name, table_width, column, owns_table
+        self.norm_name = norm_name
+        self.gate = Linear([gate_name], [dim], width)
+        self.proj = Linear([proj_name], [width], dim)
+        self.table = self.weight = None
+
+    def tensor_specs(self):
+        specs = [TensorSpec(self.table_name, (self.vocab, self.table_width))] if self.owns_table else []
+        return specs + self.gate.tensor_specs() + self.proj.tensor_specs() + [TensorSpec(self.norm_name, (self.width,), init="norm_weight")]
+
+    def elements_read_per_step(self) -> int:
+        return 2 * self.dim * self.width + self.width      # a step reads a table row per token, not the table
+
+    def bind(self, tensors, dtype, device):
+        self.gate.bind(tensors, dtype, device)
+        self.proj.bind(tensors, dtype, device)
+        self.table = tensors[self.table_name]
+        self.weight = tensors[self.norm_name].float().contiguous()
+        if self.table.dtype != dtype:
+            raise ValueError(f"the table {self.table_name} is {self.table.dtype}, the engine runs in {dtype}")
+
+    def forward(self, residual, delta, ctx) -> None:
+        k = ctx.kernels.gate
+        T = residual.shape[0]
+        xb = torch.empty((T, self.width), dtype=ctx.dtype, device=residual.device)
+        k.add_cast(residual, delta, xb)                                  # the stream takes the sublayer's output; xb = its rounding
+        a = self.gate.forward(xb, ctx)
+        g = torch.empty((T, self.dim), dtype=ctx.dtype, device=residual.device)
+        k.gelu_mul_rows(a, ctx.token_ids, self.table, self.column, g)
+        y = self.proj.forward(g, ctx, out_dtype=torch.float32, partials_ok=True)
+        k.add_rms_normed(residual, y, self.weight, self.eps)
+
+
+STREAM_INPUTS.register("token_side", TokenSideInput)
