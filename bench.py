@@ -503,7 +503,32 @@ def muvorax_config(z):
     return {"architecture": "Muvorax", "layers": layers, "norm": {"eps": 1e-6}, "vocab": DESIGN_VOCAB, "width": W}
 
 
-DESIGNS = {"sozilix": (DESIGN_SIZES, sozilix_config, 3), "muvorax": (MUVORAX_SIZES, muvorax_config, 6)}
+# The Belasun decoder (chunked grouped-query attention behind short convolutions, a whole-projection query/key norm
+# and a gate per head; routed experts with a clamped gate in every layer; a per-layer input from the token) at
+# layer sizes that resemble real models of its kinds: heads of 128 of which the first 64 dims turn, chunks of 1024
+# (2048) positions, 32 (64) experts of which 4 (6) are used. The Llama decoder beside it has the same width, depth
+# and heads, a sliding window as long as a chunk, and a dense feed-forward as wide as a token's experts together.
+BELASUN_SIZES = {
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, vdim=128, rot_dims=64, chunk=1024, conv=4, experts=32, top=4,
+                  expert_ff=704, side=128, layers=4),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, rot_dims=64, chunk=2048, conv=4, experts=64, top=6,
+                  expert_ff=1408, side=256, layers=4),
+}
+for _z in BELASUN_SIZES.values():
+    _z.update(window=_z["chunk"], ff=_z["top"] * _z["expert_ff"], groups=1)
+
+
+def belasun_config(z):
+    mixer = {"conv": z["conv"], "dim": z["dim"], "heads": z["heads"], "kv_heads": z["kv_heads"], "mask": {"size": z["chunk"]},
+             "rot": {"base": 10000.0, "dims": z["rot_dims"], "scaling": {"factor": 8.0, "high": 4.0, "low": 1.0, "original": 8192}},
+             "scale": z["dim"] ** -0.5, "vdim": z["vdim"]}
+    moe = {"expert": {"ff": z["expert_ff"], "limit": 7.0}, "kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}}
+    return {"architecture": "Belasun", "layers": [{"type": "attention", "mixer": mixer, "mlp": moe}] * z["layers"],
+            "logit_softcap": 30.0, "norm": {"eps": 1e-6}, "token_side": {"dim": z["side"]}, "vocab": DESIGN_VOCAB, "width": z["width"]}
+
+
+DESIGNS = {"sozilix": (DESIGN_SIZES, sozilix_config, 3), "muvorax": (MUVORAX_SIZES, muvorax_config, 6),
+           "belasun": (BELASUN_SIZES, belasun_config, 4)}
 
 
 def llama_like(z, max_positions, layers_per_group=3):
