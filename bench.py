@@ -598,6 +598,7 @@ def sequence_kernels_alone(args):
         pass
 
     def timed(launch, n_sets, reps=8):
+        torch.cuda.synchronize()          # the inputs were filled on the current stream; the launches run on another
         side = torch.cuda.Stream()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(side):
@@ -718,6 +719,7 @@ def mix_kernels_alone(args):
     E, top, F = z["experts"], z["top"], z["expert_ff"]
 
     def timed(launch, n_sets, reps=8):
+        torch.cuda.synchronize()          # the inputs were filled on the current stream; the launches run on another
         side = torch.cuda.Stream()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(side):
@@ -857,6 +859,188 @@ def mix_kernels_alone(args):
     return 0
 
 
+def gate_kernels_alone(args):
+    """The kernels of the Belasun decoder's layers, each alone at BELASUN_SIZES[--design-sizes or w2048] and, where
+    another decoder has a kernel of the same kind, that one beside it on the same rows: a prompt of --prefill-tokens
+    rows and a decode step of --batch rows at --context; a JSON line each with the time (CUDA events around a captured
+    run of launches whose inputs rotate through more than L2 holds where they are small) and what it is of the HBM copy
+    rate (bf16 tensor rate for the grouped products and the prompt's attention)."""
+    import torch
+    from types import SimpleNamespace
+    from scriptling_llm_lib_b200.csrc.bindings import KernelSet
+    pk = peaks()
+    z = BELASUN_SIZES[(args.design_sizes or "w2048").split(",")[0]]
+    dt = torch.bfloat16
+    ks = KernelSet(dt)
+    dev = "cuda"
+    esz = 2
+    W, H, G, D, V, rot, chunk, taps = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["rot_dims"], z["chunk"], z["conv"]
+    E, top, F, side = z["experts"], z["top"], z["expert_ff"], z["side"]
+    qw, kw, vw = H * D, G * D, G * V
+    Cw = qw + kw + vw
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+
+    def timed(launch, n_sets, reps=8):
+        torch.cuda.synchronize()          # the inputs were filled on the current stream; the launches run on another
+        side_stream = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side_stream):
+            for i in range(2):
+                launch(i % n_sets)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side_stream):
+                for i in range(reps):
+                    launch(i % n_sets)
+        for _ in range(2):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(3):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (3 * reps) * 1e3
+
+    def report(name, rows, us, nbytes=None, flops=None, like=None):
+        rec = {"kernel": name, "rows": rows, "us": round(us, 1)}
+        if like is not None:
+            rec["like"] = like
+        if nbytes is not None:
+            rec.update(gbs=round(nbytes / us / 1e3, 1), of_hbm=round(nbytes / us / 1e3 / pk["hbm_gbs"], 3))
+        if flops is not None:
+            rec.update(tflops=round(flops / us / 1e6, 1), of_bf16=round(flops / us / 1e6 / pk["bf16_tflops"], 3))
+        print(json.dumps(rec), flush=True)
+
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    for label, lens, ctxlen in (("prompt", [args.prefill_tokens], args.prefill_tokens), ("decode", [1] * args.batch, args.context)):
+        T, B = sum(lens), len(lens)
+        start = [0]
+        for n in lens:
+            start.append(start[-1] + n)
+        pages = -(-ctxlen // 64)
+        pos0 = torch.zeros(B, dtype=torch.int32, device=dev) if T != B else torch.full((B,), ctxlen - 1, dtype=torch.int32, device=dev)
+        c = SimpleNamespace(
+            seq_start=torch.tensor(start, dtype=torch.int32, device=dev),
+            tok_seq=torch.repeat_interleave(torch.arange(B, dtype=torch.int32, device=dev), torch.tensor(lens, device=dev)).int(),
+            slots=torch.arange(B, dtype=torch.int32, device=dev), n_seqs=B, max_new=max(lens), engine=SimpleNamespace(sm_count=sms),
+            seq_pos0=pos0,
+            tok_pos=(torch.arange(T, dtype=torch.int32, device=dev) if T != B else pos0.clone()))
+        n_sets = 4 if T > 64 else 24
+        table = torch.arange(B * pages, dtype=torch.int32, device=dev).view(B, pages).contiguous()
+        kp = torch.randn(B * pages + 1, G, 64, D, device=dev).to(dt)
+        vp = torch.randn(B * pages + 1, G, 64, V, device=dev).to(dt)
+        cs = torch.randn(ctxlen + 1, rot // 2, 2, device=dev)
+        # ---- the short convolution behind the projections: element type in, float32 out, the state kept
+        ys = [(torch.randn(T, Cw + H, device=dev) * 0.5).to(dt) for _ in range(n_sets)]
+        wc = torch.randn(Cw, taps, device=dev).to(dt)
+        st = torch.zeros(B + 1, taps - 1, Cw, device=dev)
+        cf = [torch.empty(T, Cw, device=dev) for _ in range(n_sets)]
+        us = timed(lambda i: ks.seq.causal_conv(ys[i][:, :Cw], wc, st, c, cf[i], taps), n_sets)
+        report(f"causal_conv {taps} taps, width {Cw} ({label})", T, us, nbytes=T * Cw * (esz + 4) + (2 * B * (taps - 1) * Cw * 4 if T == B else 0))
+        # ---- norm over the whole projection + rotation + cache write, beside the rotation + cache write of a plain layer
+        qn, kn = torch.ones(qw, device=dev), torch.ones(kw, device=dev)
+        q = torch.empty(T, qw, dtype=dt, device=dev)
+        us = timed(lambda i: ks.gate.qk_norm_store(cf[i], q, c.tok_pos, c.tok_seq, table, cs, kp, vp, H, G, D, V, rot, False, qn, kn, 1e-6), n_sets)
+        report(f"qk_norm_store ({label})", T, us, nbytes=T * Cw * (4 + esz))
+        cs_full = torch.randn(ctxlen + 1, D // 2, 2, device=dev)
+        if D == V:
+            us = timed(lambda i: ks.rope_kv_write(ys[i], c.tok_pos, c.tok_seq, table, cs_full, kp, vp, H, G, D, D, False), n_sets)
+            report(f"rope_kv_write ({label})", T, us, nbytes=T * (2 * (qw + kw) + 2 * vw) * esz, like="qk_norm_store")
+        # ---- the gate per head, beside the gated read-out norm of a linear-attention layer
+        o = torch.empty(T, H * V, dtype=dt, device=dev)
+        us = timed(lambda i: ks.gate.head_gate(o, ys[i][:, Cw:], H, V), n_sets)
+        report(f"head_gate ({label})", T, us, nbytes=2 * T * H * V * esz)
+        # ---- attention over the keys of the query's chunk, beside a sliding window of the same length
+        if T != B:
+            if D in ks.prefill_attention_tc.HEAD_DIMS and D == V:
+                for span, name, like in ((-chunk, f"chunks of {chunk}", None), (chunk, f"window of {chunk}", "chunks")):
+                    seen = sum((p % chunk if span < 0 else min(p, chunk - 1)) + 1 for p in range(T))
+                    us = timed(lambda i: ks.prefill_attention_tc.attn(q, o, c.seq_start, c.seq_pos0, table, kp, vp, B, T, H, G, D, span,
+                                                                      D ** -0.5, err), 1)
+                    report(f"attn_prefill {H}/{G} heads of {D}, {name} ({label})", T, us, flops=4 * H * D * seen, like=like)
+        elif D in ks.decode.HEAD_DIMS and D == V:
+            n_split = ks.decode.attention_splits(B, H, G, D, pages, sms)
+            scratch = torch.empty(B * H * n_split * (D + 2), dtype=torch.float32, device=dev)
+            tickets = torch.zeros(B * G, dtype=torch.int32, device=dev)
+            for span, name, like in ((-chunk, f"chunks of {chunk}", None), (chunk, f"window of {chunk}", "chunks")):
+                seen = ((ctxlen - 1) % chunk if span < 0 else min(ctxlen - 1, chunk - 1)) + 1
+                us = timed(lambda i: ks.decode.attn_decode(q, o, c.seq_pos0, table, kp, vp, scratch, B, H, G, D, span, D ** -0.5,
+                                                           n_split, tickets=tickets), 1)
+                report(f"attn_decode {H}/{G} heads of {D}, {name}, {n_split} splits ({label})", T, us, nbytes=B * seen * G * (D + V) * esz, like=like)
+        # ---- the router, beside the router with runs of experts
+        zl = torch.randn(T, E, device=dev)
+        corr = torch.zeros(E, device=dev)
+        idx = torch.empty(T, top, dtype=torch.int32, device=dev)
+        wgt = torch.empty(T, top, device=dev)
+        us = timed(lambda i: ks.mix.moe_route(zl, corr, idx, wgt, 1, 1, top, 1.0, top_softmax=True), 1)
+        report(f"moe_route top_softmax, {top} of {E} ({label})", T, us)
+        us = timed(lambda i: ks.mix.moe_route(zl, corr, idx, wgt, 1, 1, top, 1.0), 1)
+        report(f"moe_route grouped_sigmoid, {top} of {E} ({label})", T, us, like="moe_route top_softmax")
+        ks.mix.moe_route(zl, corr, idx, wgt, 1, 1, top, 1.0, top_softmax=True)
+        # ---- the experts: gate and up rows in tiles of 16 with the clamped gate, beside up rows with the square of relu
+        h = (torch.randn(T, W, device=dev) * 0.5).to(dt)
+        w_gu = (torch.randn(E, 2 * F, W, device=dev) * 0.02).to(dt)
+        w_down = (torch.randn(E, W, F, device=dev) * 0.02).to(dt)
+        pairs = T * top
+        if pairs <= 64:
+            hid = torch.empty(pairs, F, dtype=dt, device=dev)
+            out = torch.empty(top, T, W, device=dev)
+            us = timed(lambda i: ks.mix.moe_pairs(h, w_gu, w_down, idx, wgt, hid, out, glu=(7.0, 1.702), tiled=True), 1)
+            report(f"moe_pairs clamped gate, {pairs} pairs, experts {W} x {F} ({label})", T, us, nbytes=pairs * 3 * F * W * esz)
+            w_u1 = w_gu[:, :F].contiguous()
+            us = timed(lambda i: ks.mix.moe_pairs(h, w_u1, w_down, idx, wgt, hid, out), 1)
+            report(f"moe_pairs relu^2 ({label})", T, us, nbytes=pairs * 2 * F * W * esz, like="moe_pairs clamped gate")
+        else:
+            rows = -(-(pairs + E * 127) // 128) * 128
+            counts = torch.zeros(E, dtype=torch.int32, device=dev)
+            offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+            por = torch.empty(rows, dtype=torch.int32, device=dev)
+            rop = torch.empty(pairs, dtype=torch.int32, device=dev)
+            tg = torch.empty(rows // 128, dtype=torch.int32, device=dev)
+            xs2 = torch.empty(rows, W, dtype=dt, device=dev)
+            hid = torch.empty(rows, F, dtype=dt, device=dev)
+            raw = torch.empty(rows, 2 * F, dtype=dt, device=dev)
+            ys2 = torch.empty(rows, W, device=dev)
+            out = torch.empty(T, W, device=dev)
+            tc = ks.tensor_core
+            ks.mix.moe_group_rows(idx, counts, offsets, por, rop, tg, pad=128)
+            ks.mix.moe_gather_rows(h, por, top, xs2)
+            us = timed(lambda i: tc.gemm_grouped(xs2, w_gu, hid, tg, err, rows_used=offsets[E:], glu=(7.0, 1.702)), 1)
+            report(f"gemm_grouped gate|up with the clamped gate, {rows} rows for {pairs} pairs ({label})", T, us, flops=4 * pairs * F * W)
+            us = timed(lambda i: (tc.gemm_grouped(xs2, w_gu, raw, tg, err, rows_used=offsets[E:]),
+                                  ks.mix.glu_clamp(raw, hid, 7.0, 1.702, rows_used=offsets[E:], tiled=True)), 1)
+            report(f"gemm_grouped gate|up, then glu_clamp in a pass of its own ({label})", T, us, flops=4 * pairs * F * W)
+            w_u2 = w_gu.view(E * 2, F, W)
+            us = timed(lambda i: tc.gemm_grouped(xs2, w_u2, hid, tg, err, act="relu_squared", rows_used=offsets[E:]), 1)
+            report(f"gemm_grouped up with relu^2 ({label})", T, us, flops=2 * pairs * F * W, like="gemm_grouped gate|up")
+            us = timed(lambda i: tc.gemm_grouped(hid, w_down, ys2, tg, err, rows_used=offsets[E:]), 1)
+            report(f"gemm_grouped down ({label})", T, us, flops=2 * pairs * F * W)
+        # ---- the input from the token: the stream takes the sublayer, gelu(a) * e, the normed addend; beside the sum + norm of every layer
+        x32 = [torch.randn(T, W, device=dev) for _ in range(n_sets)]
+        d32 = [torch.randn(T, W, device=dev) for _ in range(n_sets)]
+        xb = torch.empty(T, W, dtype=dt, device=dev)
+        us = timed(lambda i: ks.gate.add_cast(x32[i], d32[i], xb), n_sets)
+        report(f"add_cast ({label})", T, us, nbytes=T * W * (4 + 4 + 4 + esz))
+        a = (torch.randn(T, side, device=dev)).to(dt)
+        tbl = torch.randn(DESIGN_VOCAB, z["layers"] * side, device=dev).to(dt)
+        ids = torch.randint(0, DESIGN_VOCAB, (T,), dtype=torch.int32, device=dev)
+        g = torch.empty(T, side, dtype=dt, device=dev)
+        us = timed(lambda i: ks.gate.gelu_mul_rows(a, ids, tbl, side, g), 1)
+        report(f"gelu_mul_rows width {side} ({label})", T, us, nbytes=3 * T * side * esz)
+        wn = torch.ones(W, device=dev)
+        us = timed(lambda i: ks.gate.add_rms_normed(x32[i], d32[i], wn, 1e-6), n_sets)
+        report(f"add_rms_normed ({label})", T, us, nbytes=T * W * (4 + 4 + 4))
+        wnb = torch.ones(W, device=dev).to(dt)
+        ad = (torch.randn(T, W, device=dev) * 0.5).to(dt)
+        us = timed(lambda i: ks.add_rmsnorm(x32[i], ad, None, wnb, xb, 1e-6), n_sets)
+        report(f"add_rmsnorm ({label})", T, us, nbytes=T * W * (4 + 4 + esz + esz), like="add_rms_normed, add_cast")
+        lg = torch.randn(max(B, 1), DESIGN_VOCAB, device=dev)
+        us = timed(lambda i: ks.gate.softcap(lg, 30.0), 1)
+        report(f"softcap {lg.shape[0]} x {DESIGN_VOCAB} ({label})", T, us, nbytes=2 * lg.numel() * 4)
+    return 0
+
+
 def kernel_alone(args):
     """One decode kernel by itself, as profiles/ quotes it: launched back to back in a CUDA graph over
     inputs that rotate through more bytes than L2 holds, timed with CUDA events; one JSON line per case.
@@ -873,6 +1057,7 @@ def kernel_alone(args):
     sms = torch.cuda.get_device_properties(0).multi_processor_count
 
     def timed(launch, n_sets, reps=24):
+        torch.cuda.synchronize()          # the inputs were filled on the current stream; the launches run on another
         side = torch.cuda.Stream()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(side):
@@ -962,11 +1147,12 @@ def main():
     ap.add_argument("--no-shapes", dest="shapes", action="store_false", help="skip the Llama-3.2-1B and Llama-3.1-8B sizes")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
                     help="run one part only (a small case to profile); the JSON line then holds that part alone")
-    ap.add_argument("--kernel", default=None, choices=["attn_decode", "gemm_small_m", "sequence", "mix"],
+    ap.add_argument("--kernel", default=None, choices=["attn_decode", "gemm_small_m", "sequence", "mix", "gate"],
                     help="time one decode kernel alone at --shape, --batch (and --context) instead of the model; 'sequence': "
                          "the kernels of the mixers with state at --design-sizes, for a prompt and for a decode step; 'mix': "
                          "the same for the kernels of latent attention, decayed linear attention, the selective scan and "
-                         "routed experts")
+                         "routed experts; 'gate': the same for the kernels of the Belasun decoder's layers (convolution behind "
+                         "the projections, whole-projection norm, gate per head, chunked attention, gated experts, token input)")
     ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="measure this design's prompt step and decoding at a few real layer sizes beside the Llama decoder "
                          "of equal size (--prefill-tokens, --batch, --context, --steps, --dtype, --only apply) instead of the "
@@ -983,6 +1169,8 @@ def main():
     args.warmup = max(3, args.warmup)
     if args.kernel == "sequence":
         return sequence_kernels_alone(args)
+    if args.kernel == "gate":
+        return gate_kernels_alone(args)
     if args.kernel == "mix":
         return mix_kernels_alone(args)
     if args.kernel is not None:

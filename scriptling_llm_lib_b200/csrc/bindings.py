@@ -348,20 +348,26 @@ class TensorCoreGemm:
 
     ACTS = {None: 0, "gelu_tanh": 1, "relu_squared": 2, "silu": 3}
 
-    def gemm_grouped(self, a, w, out, tile_group, err_flag, act=None, rows_used=None):
+    def gemm_grouped(self, a, w, out, tile_group, err_flag, act=None, rows_used=None, glu=None):
         """out[M, N] = act(a[M, K] @ w[g]^T) with w [G, N, K] and the 128 rows of `a` from row 128 t on multiplied by
         matrix tile_group[t] (int32 on the device, M / 128 entries): rows laid out so that no 128 hold two groups.
-        rows_used: an int32 on the device (one element), how many of the M rows hold anything; the rest is not worked."""
+        rows_used: an int32 on the device (one element), how many of the M rows hold anything; the rest is not worked.
+        `glu` = (limit, alpha): every matrix's N rows are tiles of 8 gate rows and their 8 up rows, and out [M, N / 2]
+        (bfloat16) receives the clamped gate of each pair of sums, g' * sigmoid(alpha g') * (u' + 1)."""
         M, K = a.shape
         G, N = w.shape[0], w.shape[1]
-        if (w.dim() != 3 or w.shape[2] != K or tuple(out.shape) != (M, N) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16
+        if glu is not None and (act is not None or N % 16 or out.dtype != torch.bfloat16 or not glu[0] > 0):
+            raise KernelError(f"gemm_grouped with a gate: {N} stacked rows a matrix, out {out.dtype}, act {act}, limit {glu[0]}")
+        if (w.dim() != 3 or w.shape[2] != K or tuple(out.shape) != (M, N // 2 if glu is not None else N)
+                or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16
                 or out.dtype not in (torch.bfloat16, torch.float32) or tile_group.shape[0] * 128 < M):
             raise KernelError(f"gemm_grouped shapes: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
         fn = self.lib.sllm_gemm_tc_grouped_bf16
         fn.restype = c_int
         _check(fn(_ptr(a, torch.bfloat16, "a"), _ptr(w, torch.bfloat16, "w"), _ptr(out, None, "out"), c_int(M), c_int(N), c_int(K),
-                  c_int(K), c_int(K), c_int(N), c_int(1 if out.dtype == torch.float32 else 0), _ptr(tile_group, torch.int32, "tile_group"),
-                  c_int(G), c_int(self.ACTS[act]), _ptr(rows_used, torch.int32, "rows_used"),
+                  c_int(K), c_int(K), c_int(out.shape[1]), c_int(1 if out.dtype == torch.float32 else 0),
+                  _ptr(tile_group, torch.int32, "tile_group"), c_int(G), c_int(self.ACTS[act]), _ptr(rows_used, torch.int32, "rows_used"),
+                  c_float(0.0 if glu is None else glu[0]), c_float(0.0 if glu is None else glu[1]),
                   _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_grouped")
 
     def gemm_act(self, a, w, out, err_flag, act: str):
@@ -886,25 +892,27 @@ class MixKernels:
                                      c_int(n_groups), c_int(keep), c_int(top), c_float(scale), c_int(1 if top_softmax else 0),
                                      _stream()), "moe_route")
 
-    def moe_pairs(self, h, wup, wdown, idx, wgt, hid, out, glu=None):
+    def moe_pairs(self, h, wup, wdown, idx, wgt, hid, out, glu=None, tiled=False):
         """wup [E, F, K], wdown [E, N, F]; out float32 [top, T, N] partial sums over a token's chosen experts.
-        `glu` = (limit, alpha): wup is [E, 2 F, K] (gate rows, then up rows) and the clamped gate is the activation."""
+        `glu` = (limit, alpha): wup is [E, 2 F, K] (gate rows, then up rows; `tiled`: 8 gate rows and their 8 up rows in
+        turn) and the clamped gate is the activation."""
         T, K = h.shape
         top = idx.shape[1]
         F = wdown.shape[2]
         _check(self._fn("moe_pairs")(self._view(h, "h"), c_int(h.stride(0)), _ptr(wup, self.dtype, "wup"),
                                      _ptr(wdown, self.dtype, "wdown"), _ptr(idx, torch.int32, "idx"), _ptr(wgt, torch.float32, "wgt"),
                                      _ptr(hid, self.dtype, "hid"), _ptr(out, torch.float32, "out"), c_int(T), c_int(top), c_int(K),
-                                     c_int(F), c_int(wdown.shape[1]), c_int(0 if glu is None else 1),
+                                     c_int(F), c_int(wdown.shape[1]), c_int(0 if glu is None else 2 if tiled else 1),
                                      c_float(0.0 if glu is None else glu[0]), c_float(0.0 if glu is None else glu[1]), _stream()),
                "moe_pairs")
 
-    def glu_clamp(self, gu, out, limit, alpha, rows_used=None):
-        """out [rows, F] = the clamped gate of gu [rows, 2 F] (F gate sums, then F up sums a row): g' * sigmoid(alpha g') *
-        (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit). `rows_used`: an int32 on the device, rows from there on stay."""
+    def glu_clamp(self, gu, out, limit, alpha, rows_used=None, tiled=False):
+        """out [rows, F] = the clamped gate of gu [rows, 2 F] (F gate sums, then F up sums a row; `tiled`: 8 and 8 in turn):
+        g' * sigmoid(alpha g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit). `rows_used`: an int32 on the
+        device, rows from there on stay."""
         _check(self._fn("glu_clamp")(_ptr(gu, self.dtype, "gu"), _ptr(out, self.dtype, "out"), c_int(out.shape[0]),
                                      c_int(out.shape[1]), c_float(limit), c_float(alpha), _ptr(rows_used, torch.int32, "rows_used"),
-                                     _stream()), "glu_clamp")
+                                     c_int(1 if tiled else 0), _stream()), "glu_clamp")
 
     def moe_group_rows(self, idx, counts, offsets, pair_of_row, row_of_pair=None, tile_group=None, pad=1):
         """Groups the (token, expert) pairs of idx [T, top] by expert. counts int32 [E] must be zero and is left
@@ -919,9 +927,10 @@ class MixKernels:
                                           _stream()), "moe_group_rows")
         LAUNCHES[0] += 4
 
-    def moe_grouped(self, h, wup, wdown, wgt, offsets, pair_of_row, hid, out, glu=None, raw=None):
+    def moe_grouped(self, h, wup, wdown, wgt, offsets, pair_of_row, hid, out, glu=None, raw=None, tiled=False):
         """The experts' products over rows grouped without padding (`moe_group_rows` with pad 1), float32 sums on
-        the FMA units; out float32 [top, T, N]. `glu` = (limit, alpha) with `raw` [T * top, 2 F] scratch: gated experts."""
+        the FMA units; out float32 [top, T, N]. `glu` = (limit, alpha) with `raw` [T * top, 2 F] scratch: gated experts
+        (`tiled` as for `moe_pairs`)."""
         T, K = h.shape
         top = wgt.shape[1]
         _check(self._fn("moe_grouped")(self._view(h, "h"), c_int(h.stride(0)), _ptr(wup, self.dtype, "wup"),
@@ -929,7 +938,7 @@ class MixKernels:
                                        _ptr(offsets, torch.int32, "offsets"), _ptr(pair_of_row, torch.int32, "pair_of_row"),
                                        _ptr(hid, self.dtype, "hid"), _ptr(out, torch.float32, "out"), c_int(T), c_int(top),
                                        c_int(wup.shape[0]), c_int(K), c_int(wdown.shape[2]), c_int(wdown.shape[1]),
-                                       c_int(0 if glu is None else 1), c_float(0.0 if glu is None else glu[0]),
+                                       c_int(0 if glu is None else 2 if tiled else 1), c_float(0.0 if glu is None else glu[0]),
                                        c_float(0.0 if glu is None else glu[1]), _ptr(raw, self.dtype, "raw"), _stream()),
                "moe_grouped")
         LAUNCHES[0] += 1

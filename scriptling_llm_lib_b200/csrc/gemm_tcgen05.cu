@@ -53,6 +53,9 @@ struct TcFold {
   // an activation applied to the float sums before they are stored (the plain store only): 0 none, 1 the tanh form of
   // gelu, 2 the square of relu, 3 silu
   int act;
+  // the gated store (TC_EPI_SWIGLU): glu_limit > 0 makes the gate the clamped one, g' * sigmoid(glu_alpha g') * (u' + 1)
+  // with g' = min(g, limit) and u' = clamp(u, -limit, limit); 0: silu(g) * u
+  float glu_limit, glu_alpha;
 };
 
 __device__ __forceinline__ void tc_act32(uint32_t (&r)[32], int act) {
@@ -117,9 +120,11 @@ __device__ __forceinline__ void qkv_store32(const TcRope& rp, void* C, int ldc, 
 }
 
 // Writes 32 consecutive accumulator columns of one row. EPI_STORE: as they are; EPI_SWIGLU: the 32
-// columns are 8 gate, 8 up, 8 gate, 8 up, and 16 gated values go to column (col / 2).
+// columns are 8 gate, 8 up, 8 gate, 8 up, and 16 gated values go to column (col / 2): silu(g) * u, or with
+// limit > 0 the clamped gate (see TcFold).
 template <int EPI>
-__device__ __forceinline__ void tc_store_row(void* C, int row, int col, int N, int ldc, int out_f32, const uint32_t (&r)[32]) {
+__device__ __forceinline__ void tc_store_row(void* C, int row, int col, int N, int ldc, int out_f32, const uint32_t (&r)[32],
+                                             float limit = 0.f, float alpha = 0.f) {
   if (EPI == TC_EPI_STORE) {
     if (out_f32) {
       float* dst = (float*)C + (size_t)row * ldc + col;
@@ -158,7 +163,13 @@ __device__ __forceinline__ void tc_store_row(void* C, int row, int col, int N, i
 #pragma unroll
       for (int j = 0; j < 8; j++) {
         float g = __uint_as_float(r[16 * t + j]), u = __uint_as_float(r[16 * t + 8 + j]);
-        h[8 * t + j] = __fdividef(g, 1.0f + __expf(-g)) * u;
+        if (limit > 0.f) {
+          g = fminf(g, limit);
+          u = fminf(fmaxf(u, -limit), limit);
+          h[8 * t + j] = __fdividef(g, 1.0f + __expf(-alpha * g)) * (u + 1.0f);
+        } else {
+          h[8 * t + j] = __fdividef(g, 1.0f + __expf(-g)) * u;
+        }
       }
     if (ocol + 16 <= n_out && ((uintptr_t)dst & 15) == 0) {
 #pragma unroll
@@ -269,7 +280,7 @@ __device__ __forceinline__ void tc_epilogue_tile(uint32_t acc, int q, int lane, 
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       if (owed) tc_scale32(r, rs);
       if (EPI == TC_EPI_STORE && fd.act) tc_act32(r, fd.act);
-      if (row < M) tc_store_row<EPI>(C, row, n0 + c0, N, ldc, out_f32, r);
+      if (row < M) tc_store_row<EPI>(C, row, n0 + c0, N, ldc, out_f32, r, fd.glu_limit, fd.glu_alpha);
     }
   }
 }
@@ -726,9 +737,11 @@ SLLM_EXPORT int sllm_gemm_tc_fold_bf16(const void* A, const void* B, void* C, in
 // 0 .. n_groups - 1). The caller lays the rows of A out so that no tile holds rows of two groups. The one-SM kernel
 // (tiles of 128 rows); a tile's columns beyond N read the next group's rows and are not written. m_used (or null): an
 // int on the device, the rows of A in use; the tiles behind them are left alone (their number is known on the device only).
+// glu_limit > 0 (act 0, bfloat16 out, N a multiple of 16): every matrix's rows come in tiles of 16 (8 gate rows, 8 up
+// rows) and C[M, N/2] receives the clamped gate of each pair (see TcFold).
 SLLM_EXPORT int sllm_gemm_tc_grouped_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                                          int out_f32, const int* tile_group, int n_groups, int act, const int* m_used, int* err,
-                                          cudaStream_t stream) {
+                                          int out_f32, const int* tile_group, int n_groups, int act, const int* m_used,
+                                          float glu_limit, float glu_alpha, int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || !tile_group || n_groups < 1)
     return SLLM_ERR_ARG;
@@ -746,6 +759,13 @@ SLLM_EXPORT int sllm_gemm_tc_grouped_bf16(const void* A, const void* B, void* C,
   if (rc) return rc;
   rc = tc_make_map(&mb, B, n_groups * N, K, ldb, big ? 256 : 128);
   if (rc) return rc;
+  if (glu_limit > 0.f) {
+    if (act || out_f32 || (N & 15)) return SLLM_ERR_ARG;
+    fd.glu_limit = glu_limit;
+    fd.glu_alpha = glu_alpha;
+    return big ? tc_launch<256, 4, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp, fd)
+               : tc_launch<128, 6, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp, fd);
+  }
   return big ? tc_launch<256, 4, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd)
              : tc_launch<128, 6, TC_EPI_STORE>(ma, mb, C, M, N, K, ldc, out_f32, err, stream, rp, fd);
 }

@@ -1003,21 +1003,28 @@ __device__ __forceinline__ float glu_clamp_f(float g, float u, float limit, floa
   u = fminf(fmaxf(u, -limit), limit);
   return g * sigmoid_f(alpha * g) * (u + 1.0f);
 }
-// gu [rows][2 F]: F gate sums then F up sums a row; out[row][f] = the clamped gate of (gu[row][f], gu[row][F + f]).
+// Where gate f and up f of an expert lie among its 2 F stacked rows (and among the 2 F sums of a row): F gate rows and
+// then F up rows, or `tiled` (F a multiple of 8): tiles of 16 rows, 8 gate rows and then their 8 up rows, which is the
+// order the tensor-core product's gated store wants.
+__device__ __forceinline__ int glu_gate_at(int f, int F, int tiled) { return tiled ? ((f >> 3) << 4) + (f & 7) : f; }
+__device__ __forceinline__ int glu_up_at(int f, int F, int tiled) { return tiled ? ((f >> 3) << 4) + 8 + (f & 7) : F + f; }
+// gu [rows][2 F]: the gate and up sums of a row; out[row][f] = the clamped gate of its pair f.
 // Rows from *rows_used on (when given) are left alone.
 template <typename A>
 __global__ void glu_clamp_kernel(const A* __restrict__ gu, A* __restrict__ out, int rows, int F, float limit, float alpha,
-                                 const int* __restrict__ rows_used) {
+                                 const int* __restrict__ rows_used, int tiled) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)rows * F) return;
   int r = (int)(i / F), f = (int)(i % F);
   if (rows_used && r >= *rows_used) return;
-  out[i] = from_f32<A>(glu_clamp_f(to_f32(gu[(size_t)r * 2 * F + f]), to_f32(gu[(size_t)r * 2 * F + F + f]), limit, alpha));
+  const A* g = gu + (size_t)r * 2 * F;
+  out[i] = from_f32<A>(glu_clamp_f(to_f32(g[glu_gate_at(f, F, tiled)]), to_f32(g[glu_up_at(f, F, tiled)]), limit, alpha));
 }
 
 // Few rows (a decode step): every (token, chosen expert) pair on its own, a warp per output column.
 //   up:   hid[p][f] = relu(Wup[e_p][f] . h[t_p])^2           p = t * top + k
-//         gated (Wup holds F gate rows, then F up rows, per expert): hid[p][f] = glu(Wup[e_p][f] . h, Wup[e_p][F + f] . h)
+//         gated (Wup holds F gate rows and F up rows per expert; 1: one run after the other, 2: in tiles of 16):
+//         hid[p][f] = glu(gate row f . h, up row f . h)
 //   down: out[k][t][j] = wgt[p] * (Wdown[e_p][j] . hid[p])    float32 partial sums over k, added by the reader
 template <typename A>
 __device__ __forceinline__ float warp_dot(const A* __restrict__ x, const A* __restrict__ w, int K, int lane, int vec) {
@@ -1046,8 +1053,8 @@ __global__ void __launch_bounds__(128) moe_pair_up_kernel(const A* __restrict__ 
   const A* x = h + (size_t)(p / top) * ldh;
   if (gated) {
     const A* we = wup + (size_t)idx[p] * 2 * F * K;
-    float g = warp_dot(x, we + (size_t)f * K, K, lane, vec);
-    float u = warp_dot(x, we + (size_t)(F + f) * K, K, lane, vec);
+    float g = warp_dot(x, we + (size_t)glu_gate_at(f, F, gated == 2) * K, K, lane, vec);
+    float u = warp_dot(x, we + (size_t)glu_up_at(f, F, gated == 2) * K, K, lane, vec);
     if (lane == 0) hid[(size_t)p * F + f] = from_f32<A>(glu_clamp_f(g, u, limit, alpha));
     return;
   }

@@ -17,7 +17,9 @@ Two more choices. `router="top_softmax"`: z = Wr x + bias (the stored vector is 
 `top` experts with the largest z are picked, and they count with the softmax over the picked logits alone (no
 runs, no scale). `act="clamped_glu"`: an expert has a gate and an up matrix; with g = min(Wg x, limit) and
 u = clamp(Wu x, -limit, limit) its inner vector is g * sigmoid(alpha g) * (u + 1), alpha = 1.702 unless
-given. Gate and up rows are stacked per expert ([experts, 2 ff, hidden]) and multiplied in one pass.
+given. Gate and up rows are stacked per expert ([experts, 2 ff, hidden]) and multiplied in one pass; in bfloat16
+with widths the tensor cores take they are stacked in tiles of 16 (8 gate rows, their 8 up rows), so that a long
+step's grouped product applies the gate in its epilogue and writes the inner vector only.
 
 The experts' matrices are stacked [experts, ff, hidden] and [experts, hidden, ff]. A step of few
 rows runs every (token, chosen expert) pair by itself (each streams its expert's matrices once); a
@@ -123,8 +125,15 @@ class RoutedExperts(FeedForward):
     def bind(self, tensors, dtype, device):
         self.router.bind(tensors, dtype, device)
         self.correction = tensors[self.correction_name].float().contiguous() if self.correction_name is not None else None
+        self.tiled = False
         if self.glu is not None:                                                         # [E, 2 F, hidden]: gate rows, up rows
-            self.w_up = torch.stack([torch.cat([tensors[g], tensors[u]]) for g, u in zip(self.gate_names, self.up_names)]).contiguous()
+            self.tiled = dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.F % 8 == 0
+            if self.tiled:                                                               # 8 gate rows, their 8 up rows, and so on
+                self.w_up = torch.stack([torch.stack([tensors[g].view(self.F // 8, 8, self.hidden), tensors[u].view(self.F // 8, 8, self.hidden)],
+                                                     dim=1).reshape(2 * self.F, self.hidden)
+                                         for g, u in zip(self.gate_names, self.up_names)]).contiguous()
+            else:
+                self.w_up = torch.stack([torch.cat([tensors[g], tensors[u]]) for g, u in zip(self.gate_names, self.up_names)]).contiguous()
         else:
             self.w_up = torch.stack([tensors[n] for n in self.up_names]).contiguous()    # [E, F, hidden]
         self.w_down = torch.stack([tensors[n] for n in self.down_names]).contiguous()    # [E, hidden, F]
@@ -148,7 +157,7 @@ class RoutedExperts(FeedForward):
         if pairs <= self.PAIRS_ONE_BY_ONE:
             hid = torch.empty((pairs, self.F), dtype=x.dtype, device=dev)
             out = torch.empty((self.top, T, self.hidden), dtype=torch.float32, device=dev)
-            k.moe_pairs(x, self.w_up, self.w_down, idx, wgt, hid, out, glu=self.glu)
+            k.moe_pairs(x, self.w_up, self.w_down, idx, wgt, hid, out, glu=self.glu, tiled=self.tiled)
             return out
         offsets = torch.empty((self.E + 1,), dtype=torch.int32, device=dev)
         if not self._on_tensor_cores(x):
@@ -157,7 +166,7 @@ class RoutedExperts(FeedForward):
             hid = torch.empty((pairs, self.F), dtype=x.dtype, device=dev)
             out = torch.empty((self.top, T, self.hidden), dtype=torch.float32, device=dev)
             raw = torch.empty((pairs, 2 * self.F), dtype=x.dtype, device=dev) if self.glu is not None else None
-            k.moe_grouped(x, self.w_up, self.w_down, wgt, offsets, pair_of_row, hid, out, glu=self.glu, raw=raw)
+            k.moe_grouped(x, self.w_up, self.w_down, wgt, offsets, pair_of_row, hid, out, glu=self.glu, raw=raw, tiled=self.tiled)
             return out
         # every expert's rows from a multiple of 128 on, so that a tile of the tensor-core product has one expert
         tile = 128
@@ -170,10 +179,8 @@ class RoutedExperts(FeedForward):
         k.moe_gather_rows(x, pair_of_row, self.top, xs)
         tc = ctx.kernels.tensor_core
         hid = torch.empty((rows, self.F), dtype=x.dtype, device=dev)
-        if self.glu is not None:
-            raw = torch.empty((rows, 2 * self.F), dtype=x.dtype, device=dev)
-            tc.gemm_grouped(xs, self.w_up, raw, tile_group, ctx.err_flag, rows_used=offsets[self.E:])
-            k.glu_clamp(raw, hid, self.glu[0], self.glu[1], rows_used=offsets[self.E:])
+        if self.glu is not None:      # `tiled` holds here: its conditions are those of the tensor-core path
+            tc.gemm_grouped(xs, self.w_up, hid, tile_group, ctx.err_flag, rows_used=offsets[self.E:], glu=self.glu)
         else:
             tc.gemm_grouped(xs, self.w_up, hid, tile_group, ctx.err_flag, act="relu_squared", rows_used=offsets[self.E:])
         ys = torch.empty((rows, self.hidden), dtype=torch.float32, device=dev)
