@@ -924,7 +924,7 @@ def gate_kernels_alone(args):
             seq_start=torch.tensor(start, dtype=torch.int32, device=dev),
             tok_seq=torch.repeat_interleave(torch.arange(B, dtype=torch.int32, device=dev), torch.tensor(lens, device=dev)).int(),
             slots=torch.arange(B, dtype=torch.int32, device=dev), n_seqs=B, max_new=max(lens), engine=SimpleNamespace(sm_count=sms),
-            seq_pos0=pos0,
+            seq_pos0=pos0, is_decode=T == B,
             tok_pos=(torch.arange(T, dtype=torch.int32, device=dev) if T != B else pos0.clone()))
         n_sets = 4 if T > 64 else 24
         table = torch.arange(B * pages, dtype=torch.int32, device=dev).view(B, pages).contiguous()
@@ -943,10 +943,13 @@ def gate_kernels_alone(args):
         q = torch.empty(T, qw, dtype=dt, device=dev)
         us = timed(lambda i: ks.gate.qk_norm_store(cf[i], q, c.tok_pos, c.tok_seq, table, cs, kp, vp, H, G, D, V, rot, False, qn, kn, 1e-6), n_sets)
         report(f"qk_norm_store ({label})", T, us, nbytes=T * Cw * (4 + esz))
+        us = timed(lambda i: ks.gate.conv_qk_norm_store(ys[i][:, :Cw], wc, taps, st, c, q, table, cs, kp, vp, H, G, D, V, rot, False,
+                                                        qn, kn, 1e-6), n_sets)
+        report(f"conv_qk_norm_store: the two above in one kernel ({label})", T, us, nbytes=2 * T * Cw * esz)
         cs_full = torch.randn(ctxlen + 1, D // 2, 2, device=dev)
         if D == V:
             us = timed(lambda i: ks.rope_kv_write(ys[i], c.tok_pos, c.tok_seq, table, cs_full, kp, vp, H, G, D, D, False), n_sets)
-            report(f"rope_kv_write ({label})", T, us, nbytes=T * (2 * (qw + kw) + 2 * vw) * esz, like="qk_norm_store")
+            report(f"rope_kv_write ({label})", T, us, nbytes=T * (2 * (qw + kw) + 2 * vw) * esz, like="conv_qk_norm_store")
         # ---- the gate per head, beside the gated read-out norm of a linear-attention layer
         o = torch.empty(T, H * V, dtype=dt, device=dev)
         us = timed(lambda i: ks.gate.head_gate(o, ys[i][:, Cw:], H, V), n_sets)

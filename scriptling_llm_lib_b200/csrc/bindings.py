@@ -991,6 +991,36 @@ class GateKernels:
             c_int(head_dim), c_int(v_dim), c_int(rot), c_int(1 if interleaved else 0), _ptr(q_weight, None, "q_weight"),
             _ptr(k_weight, None, "k_weight"), c_int(w_f32), c_float(eps), _stream()), "qk_norm_store")
 
+    FUSED_CONV_MAX_WIDTH = 200 * 1024 // 4      # the row stays in shared memory as floats
+
+    def conv_qk_norm_store(self, y, conv_weight, taps, state, ctx, q_out, block_table, cos_sin, kpages, vpages, n_heads, n_kv,
+                           head_dim, v_dim, rot, interleaved, q_weight, k_weight, eps):
+        """`qk_norm_store` behind a short causal convolution, in one kernel: y [T, C] (element type; a view) is the projection
+        [queries | keys | values], conv_weight [C, taps], state float32 [slots, taps - 1, C] holds each sequence's last
+        taps - 1 projected rows before the step and after it. C <= FUSED_CONV_MAX_WIDTH."""
+        T, C = y.shape
+        if (C != (n_heads + n_kv) * head_dim + n_kv * v_dim or tuple(conv_weight.shape) != (C, taps) or taps < 2
+                or tuple(state.shape[1:]) != (taps - 1, C) or C > self.FUSED_CONV_MAX_WIDTH or y.dtype != self.dtype):
+            raise KernelError(f"conv_qk_norm_store shapes: y {tuple(y.shape)} {y.dtype}, weight {tuple(conv_weight.shape)}, "
+                              f"state {tuple(state.shape)}")
+        w_f32 = 0
+        for w in (q_weight, k_weight):
+            if w is not None:
+                w_f32 = self._flag(w, "norm weight")
+        _check(self._fn("conv_qk_norm_store")(
+            self._view(y, "y"), c_int(y.stride(0)), _ptr(conv_weight, None, "conv_weight"), c_int(self._flag(conv_weight, "conv_weight")),
+            c_int(taps), _ptr(state, torch.float32, "state"), _ptr(ctx.seq_start, torch.int32, "seq_start"),
+            _ptr(ctx.tok_seq, torch.int32, "tok_seq"), _ptr(ctx.slots, torch.int32, "slots"), c_int(ctx.n_seqs),
+            c_int(1 if ctx.is_decode else 0), self._view(q_out, "q_out"), c_int(q_out.stride(0)),
+            _ptr(ctx.tok_pos, torch.int32, "tok_pos"), _ptr(block_table, torch.int32, "block_table"),
+            c_int(block_table.shape[1] if block_table is not None else 0), _ptr(cos_sin, torch.float32, "cos_sin"),
+            _ptr(kpages, self.dtype if kpages is not None else None, "kpages"),
+            _ptr(vpages, self.dtype if vpages is not None else None, "vpages"), c_int(T), c_int(n_heads), c_int(n_kv),
+            c_int(head_dim), c_int(v_dim), c_int(rot), c_int(1 if interleaved else 0), _ptr(q_weight, None, "q_weight"),
+            _ptr(k_weight, None, "k_weight"), c_int(w_f32), c_float(eps), _stream()), "conv_qk_norm_store")
+        if not ctx.is_decode:
+            LAUNCHES[0] += 1
+
     def head_gate(self, o, g, n_heads, v_dim):
         """o [T, n_heads * v_dim] (element type) *= sigmoid(g [T, n_heads]) per head; g a view, float32 or element type."""
         _check(self._fn("head_gate")(self._view(o, "o"), c_int(o.stride(0)), self._view(g, "g"), c_int(self._flag(g, "g")),

@@ -94,6 +94,214 @@ __global__ void __launch_bounds__(256) qk_norm_store_kernel(const void* __restri
   }
 }
 
+// ------------------------------------------------------------------ convolution, norm, rotation, cache write
+// The same as qk_norm_store behind a short causal convolution, one block a token and the row never leaving the
+// chip: row t of y (A, row stride ldy) is the projection [queries | keys | values] of C = (H + G) hd + G vd
+// columns; c[t][ch] = sum_j cw[ch][j] * y[t - taps + 1 + j][ch], rows before the step's first one of the sequence
+// coming from its state [slot][taps - 1][C] (float, oldest first). c is kept as floats in shared memory, the sums
+// of squares are taken on the way, then norm, rotation and stores as above. `own_state`: every sequence has one
+// row in the step, and the block moves the sequence's state on by itself (a channel's entries are read and
+// written by one thread); otherwise conv_state_kernel follows.
+struct ConvNormArgs {
+  const void* y; int ldy;
+  const void* cw; int cw_f32; int taps;
+  float* state; const int* seq_start; const int* tok_seq; const int* slots; int own_state;
+  void* q_out; int ldq;
+  const int* tok_pos; const int* block_table; int max_pages; const float2* cs;
+  void* kpages; void* vpages;
+  int H, G, hd, vd, rot, interleaved;
+  const void* qw; const void* kw; int w_f32; float eps;
+};
+
+__device__ __forceinline__ void st2(float* p, float a, float b) { *(float2*)p = make_float2(a, b); }
+__device__ __forceinline__ void st2(bf16* p, float a, float b) { *(__nv_bfloat162*)p = __floats2bfloat162_rn(a, b); }
+
+template <typename A> __device__ __forceinline__ float4 ld4f(const void* p, int is_f32, size_t i) {
+  return is_f32 ? ld4((const float*)p + i) : ld4((const A*)p + i);
+}
+
+// Four channels from c on with a number of taps known to the compiler: every load is issued before the first sum.
+template <typename A, int TAPS>
+__device__ __forceinline__ float4 conv_four(const ConvNormArgs& p, const A* __restrict__ y, float* st, int t, int first, int C, int c) {
+  constexpr int HIST = TAPS - 1;
+  float4 v[TAPS];
+  float w[4 * TAPS];                           // the four channels' taps lie one behind the other
+#pragma unroll
+  for (int j = 0; j < TAPS; j++) {
+    int s = t - HIST + j;
+    v[j] = s >= first ? ld4(y + (size_t)s * p.ldy + c) : *(const float4*)(st + (size_t)(HIST + (s - first)) * C + c);
+  }
+#pragma unroll
+  for (int m = 0; m < TAPS; m++) {
+    float4 q = ld4f<A>(p.cw, p.cw_f32, (size_t)c * TAPS + 4 * m);
+    w[4 * m] = q.x; w[4 * m + 1] = q.y; w[4 * m + 2] = q.z; w[4 * m + 3] = q.w;
+  }
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int j = 0; j < TAPS; j++) {
+    acc.x += w[j] * v[j].x;
+    acc.y += w[TAPS + j] * v[j].y;
+    acc.z += w[2 * TAPS + j] * v[j].z;
+    acc.w += w[3 * TAPS + j] * v[j].w;
+  }
+  if (p.own_state) {
+#pragma unroll
+    for (int j = 1; j < TAPS; j++) *(float4*)(st + (size_t)(j - 1) * C + c) = v[j];
+  }
+  return acc;
+}
+
+// VEC: four channels a thread. TAPS: the number of taps where the compiler knows it (VEC only), 0: p.taps.
+template <typename A, int VEC, int TAPS>
+__global__ void __launch_bounds__(256) conv_qk_norm_store_kernel(ConvNormArgs p) {
+  extern __shared__ __align__(16) float crow[];
+  __shared__ float red[32];
+  const A* y = (const A*)p.y;
+  int t = blockIdx.x;
+  int b = p.tok_seq[t];                        // the row's indices first, all at once: the stores below keep loads behind them
+  int pos = p.tok_pos[t];
+  int first = p.seq_start[b];
+  int slot = p.slots[b];
+  int page = p.G > 0 ? p.block_table[(size_t)b * p.max_pages + pos / SLLM_PAGE] : 0;
+  int hist = p.taps - 1;
+  int QW = p.H * p.hd, KW = p.G * p.hd, C = QW + KW + p.G * p.vd;
+  float* st = p.state + (size_t)slot * hist * C;
+  float ssq = 0.f, ssk = 0.f;
+  if (VEC) {                                   // four channels a thread: C, QW, KW, ldy multiples of four
+    for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (TAPS > 0) acc = conv_four<A, TAPS ? TAPS : 1>(p, y, st, t, first, C, c);
+      else
+      for (int j = 0; j < p.taps; j++) {
+        int s = t - hist + j;
+        float4 v = s >= first ? ld4(y + (size_t)s * p.ldy + c) : *(const float4*)(st + (size_t)(hist + (s - first)) * C + c);
+        acc.x += load_w(p.cw, p.cw_f32, (size_t)c * p.taps + j) * v.x;
+        acc.y += load_w(p.cw, p.cw_f32, (size_t)(c + 1) * p.taps + j) * v.y;
+        acc.z += load_w(p.cw, p.cw_f32, (size_t)(c + 2) * p.taps + j) * v.z;
+        acc.w += load_w(p.cw, p.cw_f32, (size_t)(c + 3) * p.taps + j) * v.w;
+        if (p.own_state && j > 0) *(float4*)(st + (size_t)(j - 1) * C + c) = v;      // entry j moves to j - 1
+      }
+      *(float4*)(crow + c) = acc;
+      float q = acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+      if (c < QW) ssq += q; else if (c < QW + KW) ssk += q;
+    }
+  } else {
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      float acc = 0.f;
+      for (int j = 0; j < p.taps; j++) {
+        int s = t - hist + j;
+        float v = s >= first ? to_f32(y[(size_t)s * p.ldy + c]) : st[(size_t)(hist + (s - first)) * C + c];
+        acc += load_w(p.cw, p.cw_f32, (size_t)c * p.taps + j) * v;
+        if (p.own_state && j > 0) st[(size_t)(j - 1) * C + c] = v;
+      }
+      crow[c] = acc;
+      if (c < QW) ssq += acc * acc; else if (c < QW + KW) ssk += acc * acc;
+    }
+  }
+  float rq = 1.f, rk = 1.f;
+  if (p.qw) rq = 1.0f / sqrtf(block_sum(ssq, red) / (float)QW + p.eps);
+  if (p.kw && p.G > 0) rk = 1.0f / sqrtf(block_sum(ssk, red) / (float)KW + p.eps);
+  __syncthreads();
+  size_t page_slot = (size_t)page * p.G * SLLM_PAGE + (pos % SLLM_PAGE);
+  A* q_row = (A*)p.q_out + (size_t)t * p.ldq;
+  A* kp = (A*)p.kpages;
+  A* vp = (A*)p.vpages;
+  int hd = p.hd, half = p.rot >> 1;
+  const float2* csr = p.cs + (size_t)pos * half;
+  if (VEC && (p.interleaved || !(half & 1))) {             // two neighbouring dims a thread, one store for both
+    int per = p.interleaved ? half : half >> 1;            // threads a head
+    for (int idx = threadIdx.x; idx < (p.H + p.G) * per; idx += blockDim.x) {
+      int head = idx / per, i = idx % per;
+      int col = head * hd;
+      bool is_q = head < p.H;
+      const void* w = is_q ? p.qw : p.kw;
+      int wc = is_q ? col : col - QW;
+      float r = is_q ? rq : rk;
+      A* dst = is_q ? q_row + col : kp + (page_slot + (size_t)(head - p.H) * SLLM_PAGE) * hd;
+      if (p.interleaved) {
+        float x0 = crow[col + 2 * i] * r, x1 = crow[col + 2 * i + 1] * r;
+        if (w) { x0 *= load_w(w, p.w_f32, wc + 2 * i); x1 *= load_w(w, p.w_f32, wc + 2 * i + 1); }
+        float2 a = csr[i];
+        st2(dst + 2 * i, x0 * a.x - x1 * a.y, x1 * a.x + x0 * a.y);
+      } else {
+        int i0 = 2 * i, i1 = i0 + half;
+        float xa0 = crow[col + i0] * r, xb0 = crow[col + i0 + 1] * r, xa1 = crow[col + i1] * r, xb1 = crow[col + i1 + 1] * r;
+        if (w) {
+          xa0 *= load_w(w, p.w_f32, wc + i0); xb0 *= load_w(w, p.w_f32, wc + i0 + 1);
+          xa1 *= load_w(w, p.w_f32, wc + i1); xb1 *= load_w(w, p.w_f32, wc + i1 + 1);
+        }
+        float2 a = csr[i0], bb = csr[i0 + 1];
+        st2(dst + i0, xa0 * a.x - xa1 * a.y, xb0 * bb.x - xb1 * bb.y);
+        st2(dst + i1, xa1 * a.x + xa0 * a.y, xb1 * bb.x + xb0 * bb.y);
+      }
+    }
+    int tail2 = (hd - p.rot) >> 1;                         // hd and rot are even here
+    for (int idx = threadIdx.x; idx < (p.H + p.G) * tail2; idx += blockDim.x) {
+      int head = idx / tail2, j = p.rot + 2 * (idx % tail2);
+      int col = head * hd;
+      bool is_q = head < p.H;
+      const void* w = is_q ? p.qw : p.kw;
+      float r = is_q ? rq : rk;
+      float x0 = crow[col + j] * r, x1 = crow[col + j + 1] * r;
+      if (w) { int wc = (is_q ? col : col - QW) + j; x0 *= load_w(w, p.w_f32, wc); x1 *= load_w(w, p.w_f32, wc + 1); }
+      A* dst = is_q ? q_row + col : kp + (page_slot + (size_t)(head - p.H) * SLLM_PAGE) * hd;
+      st2(dst + j, x0, x1);
+    }
+    int vd4 = p.vd >> 2;
+    for (int idx = threadIdx.x; idx < p.G * vd4; idx += blockDim.x) {
+      int g = idx / vd4, j = 4 * (idx % vd4);
+      st4(vp + (page_slot + (size_t)g * SLLM_PAGE) * p.vd + j, *(const float4*)(crow + QW + KW + g * p.vd + j));
+    }
+    return;
+  }
+  for (int idx = threadIdx.x; idx < (p.H + p.G) * half; idx += blockDim.x) {
+    int head = idx / half, i = idx % half;
+    int i0 = p.interleaved ? 2 * i : i, i1 = p.interleaved ? 2 * i + 1 : i + half;
+    int col = head * hd;
+    bool is_q = head < p.H;
+    const void* w = is_q ? p.qw : p.kw;
+    int wc = is_q ? col : col - QW;
+    float r = is_q ? rq : rk;
+    float x0 = crow[col + i0] * r, x1 = crow[col + i1] * r;
+    if (w) { x0 *= load_w(w, p.w_f32, wc + i0); x1 *= load_w(w, p.w_f32, wc + i1); }
+    float2 a = csr[i];
+    A* dst = is_q ? q_row + col : kp + (page_slot + (size_t)(head - p.H) * SLLM_PAGE) * hd;
+    dst[i0] = from_f32<A>(x0 * a.x - x1 * a.y);
+    dst[i1] = from_f32<A>(x1 * a.x + x0 * a.y);
+  }
+  int tail = hd - p.rot;
+  for (int idx = threadIdx.x; idx < (p.H + p.G) * tail; idx += blockDim.x) {
+    int head = idx / tail, j = p.rot + idx % tail;
+    int col = head * hd;
+    bool is_q = head < p.H;
+    const void* w = is_q ? p.qw : p.kw;
+    float x = crow[col + j] * (is_q ? rq : rk);
+    if (w) x *= load_w(w, p.w_f32, (is_q ? col : col - QW) + j);
+    A* dst = is_q ? q_row + col : kp + (page_slot + (size_t)(head - p.H) * SLLM_PAGE) * hd;
+    dst[j] = from_f32<A>(x);
+  }
+  for (int idx = threadIdx.x; idx < p.G * p.vd; idx += blockDim.x) {
+    int g = idx / p.vd, j = idx % p.vd;
+    vp[(page_slot + (size_t)g * SLLM_PAGE) * p.vd + j] = from_f32<A>(crow[QW + KW + idx]);
+  }
+}
+
+// After a step of several rows a sequence: the state becomes the last taps - 1 rows of [state | the step's rows].
+template <typename A>
+__global__ void conv_state_kernel(ConvNormArgs p, int n_seqs, int C) {
+  int b = blockIdx.x;
+  int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C || b >= n_seqs) return;
+  const A* y = (const A*)p.y;
+  int first = p.seq_start[b], n = p.seq_start[b + 1] - first;
+  int hist = p.taps - 1;
+  float* st = p.state + (size_t)p.slots[b] * hist * C;
+  for (int k = 0; k < hist; k++) {              // ascending: a kept entry moves down before its place is written
+    int s = n + k - hist;                       // a row of the step, or (negative) an entry of the old state
+    st[(size_t)k * C + c] = s >= 0 ? to_f32(y[(size_t)(first + s) * p.ldy + c]) : st[(size_t)(hist + s) * C + c];
+  }
+}
+
 // ------------------------------------------------------------------ a gate per head on the attention output
 // o[t][h * vd + j] *= sigmoid(g[t * ldg + h]) (g float or A), one thread per element.
 template <typename A>
@@ -107,6 +315,19 @@ __global__ void head_gate_kernel(A* __restrict__ o, int ldo, const void* __restr
   *p = from_f32<A>(to_f32(*p) * s);
 }
 
+// four neighbouring columns a thread: vd, ldo multiples of four, o aligned for the wide access
+template <typename A>
+__global__ void head_gate_vec_kernel(A* __restrict__ o, int ldo, const void* __restrict__ g, int g_f32, int ldg, int T, int H, int vd) {
+  size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  size_t wrow = (size_t)H * vd;
+  if (i >= (size_t)T * wrow) return;
+  int t = (int)(i / wrow), r = (int)(i % wrow);
+  float s = sigmoid_f(ld_flag<A>(g, g_f32, (size_t)t * ldg + r / vd));
+  A* p = o + (size_t)t * ldo + r;
+  float4 v = ld4(p);
+  st4(p, make_float4(v.x * s, v.y * s, v.z * s, v.w * s));
+}
+
 // ------------------------------------------------------------------ the stream takes its pending addend; a copy in A
 // x float [n] += sum over p < P of d[p * n + i] (d float or A; P == 0: nothing to add); xb[i] = A(x[i]).
 template <typename A>
@@ -117,6 +338,20 @@ __global__ void add_cast_kernel(float* __restrict__ x, const void* __restrict__ 
   for (int p = 0; p < P; p++) v += ld_flag<A>(d, d_f32, (size_t)p * n + i);
   if (P > 0) x[i] = v;
   xb[i] = from_f32<A>(v);
+}
+
+// four elements a thread (n a multiple of four)
+template <typename A>
+__global__ void add_cast_vec_kernel(float* __restrict__ x, const void* __restrict__ d, int d_f32, int P, A* __restrict__ xb, size_t n) {
+  size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  float4 v = *(const float4*)(x + i);
+  for (int p = 0; p < P; p++) {
+    float4 a = ld4f<A>(d, d_f32, (size_t)p * n + i);
+    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+  }
+  if (P > 0) *(float4*)(x + i) = v;
+  st4(xb + i, v);
 }
 
 // ------------------------------------------------------------------ gelu(a) * a slice of the token's table row
@@ -148,6 +383,35 @@ __global__ void add_rms_normed_kernel(float* __restrict__ x, const void* __restr
   }
   float r = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
   for (int j = threadIdx.x; j < d; j += blockDim.x) x[(size_t)t * d + j] += rowbuf[j] * r * load_w(w, w_f32, j);
+}
+
+// four columns a thread (d a multiple of four); the partial sums are added in the same order
+template <typename A>
+__global__ void add_rms_normed_vec_kernel(float* __restrict__ x, const void* __restrict__ y, int y_f32, int P, int T,
+                                          const void* __restrict__ w, int w_f32, int d, float eps) {
+  extern __shared__ __align__(16) float rowbuf[];
+  __shared__ float red[32];
+  int t = blockIdx.x;
+  float ss = 0.f;
+  for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < P; p++) {
+      float4 a = ld4f<A>(y, y_f32, ((size_t)p * T + t) * d + j);
+      v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+    }
+    *(float4*)(rowbuf + j) = v;
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  float r = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
+  for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+    float4 v = *(const float4*)(rowbuf + j);
+    float4 xv = *(const float4*)(x + (size_t)t * d + j);
+    xv.x += v.x * r * load_w(w, w_f32, j);
+    xv.y += v.y * r * load_w(w, w_f32, j + 1);
+    xv.z += v.z * r * load_w(w, w_f32, j + 2);
+    xv.w += v.w * r * load_w(w, w_f32, j + 3);
+    *(float4*)(x + (size_t)t * d + j) = xv;
+  }
 }
 
 // ------------------------------------------------------------------ cap * tanh(x / cap)

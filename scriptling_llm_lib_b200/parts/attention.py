@@ -21,8 +21,9 @@ projected rows of a sequence are its state. `qk_norm`: queries and keys are each
 square of the WHOLE projection (all heads at once) and multiplied by a weight of that size, before the
 rotation. `gate_name`: a matrix [n_heads, hidden] on the mixer's own input; head h's output is multiplied by
 the sigmoid of its logit before the output product. With `conv` or `qk_norm` the step's rows go through one
-kernel that norms, rotates and fills the cache (`qk_norm_store`), in float32 from the convolution's float32
-output; the attention kernels are the same ones.
+kernel that norms, rotates and fills the cache in float32: `conv_qk_norm_store` does the convolution too and
+keeps its float32 output on the chip (rows up to 51200 columns); `qk_norm_store` reads the float32 output of a
+convolution that ran by itself, or the projection. The attention kernels are the same ones.
 
 The position encoding is optional (`position=None`: queries and keys as projected). Storing keys
 and values in the cache is this mixer's own step, whatever the encoding: for an encoding that is a
@@ -210,7 +211,10 @@ class Attention(Mixer):
         qw, kw, vw = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim, self.n_kv_heads * self.v_dim
         y = self.qkv.forward(x, ctx)
         c = y[:, :qw + kw + vw]
-        if self.conv is not None:
+        k = ctx.kernels.gate
+        fused_conv = (self.conv is not None and self.conv.plain and c.dtype == ctx.dtype
+                      and qw + kw + vw <= k.FUSED_CONV_MAX_WIDTH)
+        if self.conv is not None and not fused_conv:
             c = self.conv.forward(c, state["conv"], ctx, torch.float32)
         rotation = self.position.rotation() if self.position is not None else None
         if self.position is not None and rotation is None:
@@ -218,8 +222,13 @@ class Attention(Mixer):
         table, rot, interleaved = rotation if rotation is not None else (None, 0, False)
         q = torch.empty((T, qw), dtype=x.dtype, device=x.device)
         eps = float(self.qk_norm["eps"]) if self.qk_norm is not None else 0.0
-        ctx.kernels.gate.qk_norm_store(c, q, ctx.tok_pos, ctx.tok_seq, block_table, table, kpages, vpages, self.n_heads,
-                                       self.n_kv_heads, self.head_dim, self.v_dim, rot, interleaved, self.q_norm_w, self.k_norm_w, eps)
+        if fused_conv:     # the convolution's output stays on the chip: one kernel from the projection to the cache
+            k.conv_qk_norm_store(c, self.conv.weight, self.conv.taps, state["conv"], ctx, q, block_table, table, kpages, vpages,
+                                 self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim, rot, interleaved, self.q_norm_w,
+                                 self.k_norm_w, eps)
+        else:
+            k.qk_norm_store(c, q, ctx.tok_pos, ctx.tok_seq, block_table, table, kpages, vpages, self.n_heads,
+                            self.n_kv_heads, self.head_dim, self.v_dim, rot, interleaved, self.q_norm_w, self.k_norm_w, eps)
         fast_decode = (ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in DecodeKernels.HEAD_DIMS
                        and not self.other_widths)
         attn = self._attend(q, x, ctx, kpages, vpages, block_table, fast_decode, None, writes)

@@ -46,6 +46,11 @@ class CausalConv:
         self.weight = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0).contiguous()
         self.bias = tensors[self.bias_name] if self.bias_name is not None else None
 
+    @property
+    def plain(self) -> bool:
+        """Taps and nothing else: no bias, no added input, no activation (what a fused consumer takes over)."""
+        return self.bias_name is None and not self.residual and self.act is None and self.taps > 1
+
     def state_need(self) -> StateNeed | None:
         return StateNeed((self.taps - 1, self.width), torch.float32) if self.taps > 1 else None
 

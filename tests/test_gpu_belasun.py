@@ -391,6 +391,24 @@ def test_the_small_kernels_against_their_formulas():
         ks.gate.head_gate(od, lg.cuda(), 3, 5)
         want = (o.double().view(7, 3, 5) * torch.sigmoid(lg.double())[:, :, None]).view(7, 15)
         assert float((od.cpu().double() - want).abs().max()) < tol
+        # the same over widths that take the four-wide kernels
+        o = torch.randn(9, 4 * 8, generator=g).to(dtype)
+        lg = torch.randn(9, 4, generator=g).to(dtype)
+        od = o.clone().cuda()
+        ks.gate.head_gate(od, lg.cuda(), 4, 8)
+        want = (o.double().view(9, 4, 8) * torch.sigmoid(lg.double())[:, :, None]).view(9, 32)
+        assert float((od.cpu().double() - want).abs().max()) < tol
+        x = torch.randn(5, 72, generator=g)
+        y = torch.randn(2, 5, 72, generator=g)
+        w = torch.randn(72, generator=g)
+        xd = x.clone().cuda()
+        ks.gate.add_rms_normed(xd, y.cuda(), w.cuda(), 1e-3)
+        assert float((xd.cpu().double() - x.double() - plain.rms_norm(y.double().sum(0), w, 1e-3)).abs().max()) < 1e-5
+        xd = x.clone().cuda()
+        xb = torch.empty((5, 72), dtype=dtype, device="cuda")
+        ks.gate.add_cast(xd, y.cuda(), xb)
+        assert float((xd.cpu().double() - x.double() - y.double().sum(0)).abs().max()) < 1e-5
+        assert float((xb.cpu().double() - xd.cpu().double()).abs().max()) < tol
         # stream += y / rms(y) * w, y as partial sums
         x = torch.randn(7, 50, generator=g)
         y = torch.randn(3, 7, 50, generator=g)
@@ -416,6 +434,61 @@ def test_the_small_kernels_against_their_formulas():
         want = plain.softcap(lgt.cpu().double(), 7.5)
         ks.gate.softcap(lgt, 7.5)
         assert float((lgt.cpu().double() - want).abs().max()) < 1e-5
+
+
+@pytest.mark.parametrize("H,G,hd,vd,rot,taps,gate_cols,interleaved", [
+    (4, 2, 16, 16, 8, 4, 4, False),      # four channels a thread, two dims a store
+    (4, 2, 16, 8, 16, 3, 0, True),       # neighbouring pairs
+    (2, 2, 12, 4, 6, 2, 0, False),       # an odd number of pairs a head: one dim a store
+    (3, 1, 5, 3, 4, 5, 3, False),        # widths that are multiples of nothing
+    (2, 1, 8, 8, 0, 4, 0, False)])       # nothing turns
+def test_convolution_norm_and_store_in_one_kernel_equal_the_two_kernels(H, G, hd, vd, rot, taps, gate_cols, interleaved):
+    """A prompt step of three sequences that have a past (one of a single row), then a decode step of the three: the
+    queries, the cache pages and the convolution's state of the one-kernel path against the convolution and the
+    norm-and-store kernel run one behind the other."""
+    from types import SimpleNamespace
+    from scriptling_llm_lib_b200.csrc.bindings import KernelSet
+    g = torch.Generator().manual_seed(31)
+    QW, KW, VW = H * hd, G * hd, G * vd
+    C = QW + KW + VW
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        ks = KernelSet(dtype)
+        wc = (torch.randn(C, taps, generator=g) * 0.5).to(dtype).cuda()
+        qn, kn = (torch.rand(QW, generator=g) + 0.5).cuda(), (torch.rand(KW, generator=g) + 0.5).cuda()
+        cs = torch.randn(300, max(rot // 2, 1), 2, generator=g).cuda()
+        slots = torch.tensor([2, 0, 3], dtype=torch.int32).cuda()
+        table = torch.tensor([[4, 1], [0, 5], [2, 3]], dtype=torch.int32).cuda()
+        state0 = torch.randn(5, taps - 1, C, generator=g).cuda()
+        outs = []
+        for fused in (False, True):
+            st = state0.clone()
+            kp = torch.zeros(7, G, 64, hd, dtype=dtype, device="cuda")
+            vp = torch.zeros(7, G, 64, vd, dtype=dtype, device="cuda")
+            got = []
+            for lens, pos0 in (([5, 1, 9], [60, 3, 17]), ([1, 1, 1], [65, 4, 26])):
+                T = sum(lens)
+                start = [0]
+                for n in lens:
+                    start.append(start[-1] + n)
+                ctx = SimpleNamespace(
+                    seq_start=torch.tensor(start, dtype=torch.int32).cuda(), n_seqs=3, slots=slots, is_decode=max(lens) == 1,
+                    tok_seq=torch.tensor([b for b, n in enumerate(lens) for _ in range(n)], dtype=torch.int32).cuda(),
+                    tok_pos=torch.tensor([pos0[b] + i for b, n in enumerate(lens) for i in range(n)], dtype=torch.int32).cuda())
+                y = torch.randn(T, C + gate_cols, generator=torch.Generator().manual_seed(T)).to(dtype).cuda()
+                q = torch.zeros(T, QW, dtype=dtype, device="cuda")
+                if fused:
+                    ks.gate.conv_qk_norm_store(y[:, :C], wc, taps, st, ctx, q, table, cs if rot else None, kp, vp, H, G, hd, vd, rot,
+                                               interleaved, qn, kn, 1e-4)
+                else:
+                    c = torch.empty(T, C, device="cuda")
+                    ks.seq.causal_conv(y[:, :C], wc, st, ctx, c, taps)
+                    ks.gate.qk_norm_store(c, q, ctx.tok_pos, ctx.tok_seq, table, cs if rot else None, kp, vp, H, G, hd, vd, rot,
+                                          interleaved, qn, kn, 1e-4)
+                got.append(q.float().cpu())
+            outs.append(got + [kp.float().cpu(), vp.float().cpu(), st.cpu()])
+        for a, b in zip(*outs):
+            assert float((a - b).abs().max()) <= tol * max(1.0, float(a.abs().max()))
+        assert float(outs[1][2].abs().max()) > 0 and float((outs[1][4] - state0.cpu()).abs().max()) > 0
 
 
 def test_experts_one_by_one_and_grouped_agree(folders):
