@@ -153,7 +153,7 @@ __device__ __forceinline__ float4 conv_four(const ConvNormArgs& p, const A* __re
 
 // VEC: four channels a thread. TAPS: the number of taps where the compiler knows it (VEC only), 0: p.taps.
 template <typename A, int VEC, int TAPS>
-__global__ void __launch_bounds__(256) conv_qk_norm_store_kernel(ConvNormArgs p) {
+__global__ void __launch_bounds__(256, 5) conv_qk_norm_store_kernel(ConvNormArgs p) {
   extern __shared__ __align__(16) float crow[];
   __shared__ float red[32];
   const A* y = (const A*)p.y;
@@ -208,50 +208,47 @@ __global__ void __launch_bounds__(256) conv_qk_norm_store_kernel(ConvNormArgs p)
   A* vp = (A*)p.vpages;
   int hd = p.hd, half = p.rot >> 1;
   const float2* csr = p.cs + (size_t)pos * half;
-  if (VEC && (p.interleaved || !(half & 1))) {             // two neighbouring dims a thread, one store for both
-    int per = p.interleaved ? half : half >> 1;            // threads a head
-    for (int idx = threadIdx.x; idx < (p.H + p.G) * per; idx += blockDim.x) {
-      int head = idx / per, i = idx % per;
+  if (VEC && (p.interleaved || !(half & 1))) {
+    // a warp a head, a lane two neighbouring dims (both in the same half of the turning part, or a pair of their own,
+    // or behind it) and one store for both: no division on the way
+    int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int head = wid; head < p.H + p.G; head += nw) {
       int col = head * hd;
       bool is_q = head < p.H;
       const void* w = is_q ? p.qw : p.kw;
       int wc = is_q ? col : col - QW;
       float r = is_q ? rq : rk;
       A* dst = is_q ? q_row + col : kp + (page_slot + (size_t)(head - p.H) * SLLM_PAGE) * hd;
-      if (p.interleaved) {
-        float x0 = crow[col + 2 * i] * r, x1 = crow[col + 2 * i + 1] * r;
-        if (w) { x0 *= load_w(w, p.w_f32, wc + 2 * i); x1 *= load_w(w, p.w_f32, wc + 2 * i + 1); }
-        float2 a = csr[i];
-        st2(dst + 2 * i, x0 * a.x - x1 * a.y, x1 * a.x + x0 * a.y);
-      } else {
-        int i0 = 2 * i, i1 = i0 + half;
-        float xa0 = crow[col + i0] * r, xb0 = crow[col + i0 + 1] * r, xa1 = crow[col + i1] * r, xb1 = crow[col + i1 + 1] * r;
-        if (w) {
-          xa0 *= load_w(w, p.w_f32, wc + i0); xb0 *= load_w(w, p.w_f32, wc + i0 + 1);
-          xa1 *= load_w(w, p.w_f32, wc + i1); xb1 *= load_w(w, p.w_f32, wc + i1 + 1);
+      for (int d = 2 * lane; d < hd; d += 64) {
+        float2 x = *(const float2*)(crow + col + d);
+        float w0 = 1.f, w1 = 1.f;
+        if (w) { w0 = load_w(w, p.w_f32, wc + d); w1 = load_w(w, p.w_f32, wc + d + 1); }
+        float o0 = x.x * r * w0, o1 = x.y * r * w1;
+        if (d < p.rot) {
+          if (p.interleaved) {
+            float2 a = csr[d >> 1];
+            float t0 = o0 * a.x - o1 * a.y;
+            o1 = o1 * a.x + o0 * a.y;
+            o0 = t0;
+          } else {
+            bool low = d < half;
+            int pd = low ? d + half : d - half;                        // the partner dims
+            float2 y = *(const float2*)(crow + col + pd);
+            float v0 = 1.f, v1 = 1.f;
+            if (w) { v0 = load_w(w, p.w_f32, wc + pd); v1 = load_w(w, p.w_f32, wc + pd + 1); }
+            float p0 = y.x * r * v0, p1 = y.y * r * v1;
+            int ci = low ? d : pd;
+            float2 a = csr[ci], bb = csr[ci + 1];
+            o0 = low ? o0 * a.x - p0 * a.y : o0 * a.x + p0 * a.y;
+            o1 = low ? o1 * bb.x - p1 * bb.y : o1 * bb.x + p1 * bb.y;
+          }
         }
-        float2 a = csr[i0], bb = csr[i0 + 1];
-        st2(dst + i0, xa0 * a.x - xa1 * a.y, xb0 * bb.x - xb1 * bb.y);
-        st2(dst + i1, xa1 * a.x + xa0 * a.y, xb1 * bb.x + xb0 * bb.y);
+        st2(dst + d, o0, o1);
       }
     }
-    int tail2 = (hd - p.rot) >> 1;                         // hd and rot are even here
-    for (int idx = threadIdx.x; idx < (p.H + p.G) * tail2; idx += blockDim.x) {
-      int head = idx / tail2, j = p.rot + 2 * (idx % tail2);
-      int col = head * hd;
-      bool is_q = head < p.H;
-      const void* w = is_q ? p.qw : p.kw;
-      float r = is_q ? rq : rk;
-      float x0 = crow[col + j] * r, x1 = crow[col + j + 1] * r;
-      if (w) { int wc = (is_q ? col : col - QW) + j; x0 *= load_w(w, p.w_f32, wc); x1 *= load_w(w, p.w_f32, wc + 1); }
-      A* dst = is_q ? q_row + col : kp + (page_slot + (size_t)(head - p.H) * SLLM_PAGE) * hd;
-      st2(dst + j, x0, x1);
-    }
-    int vd4 = p.vd >> 2;
-    for (int idx = threadIdx.x; idx < p.G * vd4; idx += blockDim.x) {
-      int g = idx / vd4, j = 4 * (idx % vd4);
-      st4(vp + (page_slot + (size_t)g * SLLM_PAGE) * p.vd + j, *(const float4*)(crow + QW + KW + g * p.vd + j));
-    }
+    for (int g = wid; g < p.G; g += nw)
+      for (int j = 4 * lane; j < p.vd; j += 128)
+        st4(vp + (page_slot + (size_t)g * SLLM_PAGE) * p.vd + j, *(const float4*)(crow + QW + KW + g * p.vd + j));
     return;
   }
   for (int idx = threadIdx.x; idx < (p.H + p.G) * half; idx += blockDim.x) {

@@ -1086,12 +1086,17 @@ __global__ void moe_count_kernel(const int* __restrict__ idx, int n_pairs, int* 
 // with rows for the tiles behind all ranges: they hold no pair).
 __global__ void moe_offsets_kernel(int* __restrict__ counts, int* __restrict__ offsets, int E, int pad,
                                    int* __restrict__ tile_group, int n_tiles) {
+  extern __shared__ int cnt[];                    // the counts fetched by all threads at once; one thread then adds them up
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    cnt[e] = counts[e];
+    counts[e] = 0;                                // reused as the fill counters of the placing pass
+  }
+  __syncthreads();
   if (threadIdx.x == 0) {
     int a = 0, t = 0;
     for (int e = 0; e < E; e++) {
       offsets[e] = a;
-      a += (counts[e] + pad - 1) / pad * pad;
-      counts[e] = 0;                              // reused as the fill counters of the placing pass
+      a += (cnt[e] + pad - 1) / pad * pad;
       if (tile_group)
         for (; t < n_tiles && t * pad < a; t++) tile_group[t] = e;
     }
@@ -1135,6 +1140,21 @@ __global__ void moe_combine_kernel(const float* __restrict__ ys, const int* __re
     float a = 0.f;
     for (int k = 0; k < top; k++) a += wgt[(size_t)t * top + k] * ys[(size_t)row_of_pair[(size_t)t * top + k] * N + j];
     out[(size_t)t * N + j] = a;
+  }
+}
+
+// the same, four columns a thread (N a multiple of four); the choices are added in the same order
+__global__ void moe_combine_vec_kernel(const float* __restrict__ ys, const int* __restrict__ row_of_pair,
+                                       const float* __restrict__ wgt, float* __restrict__ out, int top, int N) {
+  int t = blockIdx.x;
+  for (int j = threadIdx.x * 4; j < N; j += blockDim.x * 4) {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < top; k++) {
+      float w = wgt[(size_t)t * top + k];
+      float4 v = *(const float4*)(ys + (size_t)row_of_pair[(size_t)t * top + k] * N + j);
+      a.x += w * v.x; a.y += w * v.y; a.z += w * v.z; a.w += w * v.w;
+    }
+    *(float4*)(out + (size_t)t * N + j) = a;
   }
 }
 
