@@ -1035,6 +1035,8 @@ def gate_kernels_alone(args):
         us = timed(lambda i: ks.gate.add_rms_normed(x32[i], d32[i], wn, 1e-6), n_sets)
         report(f"add_rms_normed ({label})", T, us, nbytes=T * W * (4 + 4 + 4))
         wnb = torch.ones(W, device=dev).to(dt)
+        us = timed(lambda i: ks.gate.add_rms_normed(x32[i], d32[i], wn, 1e-6, norm=(wnb, 1e-6, xb)), n_sets)
+        report(f"add_rms_normed with the next norm's output ({label})", T, us, nbytes=T * W * (4 + 4 + 4 + esz))
         ad = (torch.randn(T, W, device=dev) * 0.5).to(dt)
         us = timed(lambda i: ks.add_rmsnorm(x32[i], ad, None, wnb, xb, 1e-6), n_sets)
         report(f"add_rmsnorm ({label})", T, us, nbytes=T * W * (4 + 4 + esz + esz), like="add_rms_normed, add_cast")

@@ -1043,14 +1043,23 @@ class GateKernels:
                                          _ptr(out, self.dtype, "out"), c_int(a.shape[0]), c_int(a.shape[1]), _stream()),
                "gelu_mul_rows")
 
-    def add_rms_normed(self, x, y, weight, eps):
-        """x float32 [T, d] += y / sqrt(mean(y^2) + eps) * weight; y [T, d] or [P, T, d] partial sums (float32 or element type)."""
+    def add_rms_normed(self, x, y, weight, eps, norm=None, rows=None):
+        """x float32 [T, d] += y / sqrt(mean(y^2) + eps) * weight; y [T, d] or [P, T, d] partial sums (float32 or element type).
+        `norm` = (weight2, eps2, out): in the same pass out (element type) = x / sqrt(mean(x^2) + eps2) * weight2 of the
+        stream as it then stands; with `rows` (int32 on the device) only those rows are worked on and out has a row for each."""
         P = y.shape[0] if y.dim() == 3 else 1
-        if tuple(y.shape[-2:]) != tuple(x.shape):
+        if tuple(y.shape[-2:]) != tuple(x.shape) or not y.is_contiguous() or (rows is not None and norm is None):
             raise KernelError(f"y {tuple(y.shape)} does not fit the stream {tuple(x.shape)}")
+        w2, eps2, out = norm if norm is not None else (None, 0.0, None)
+        n_out = 0 if norm is None else (x.shape[0] if rows is None else rows.shape[0])
+        if norm is not None and (tuple(out.shape) != (n_out, x.shape[1]) or not out.is_contiguous() or w2.shape[0] != x.shape[1]):
+            raise KernelError(f"the norm's output {tuple(out.shape)} does not fit {n_out} rows of the stream {tuple(x.shape)}")
         _check(self._fn("add_rms_normed")(_ptr(x, torch.float32, "x"), _ptr(y, None, "y"), c_int(self._flag(y, "y")), c_int(P),
                                           c_int(x.shape[0]), _ptr(weight, None, "weight"), c_int(self._flag(weight, "weight")),
-                                          c_int(x.shape[1]), c_float(eps), _stream()), "add_rms_normed")
+                                          c_int(x.shape[1]), c_float(eps), _ptr(rows, torch.int32, "rows"), c_int(n_out),
+                                          _ptr(w2, None, "weight2"), c_int(self._flag(w2, "weight2") if w2 is not None else 0),
+                                          c_float(eps2), _ptr(out, self.dtype if out is not None else None, "out"), _stream()),
+               "add_rms_normed")
 
     def softcap(self, x, cap):
         """x float32 = cap * tanh(x / cap), in place."""

@@ -365,12 +365,15 @@ __global__ void gelu_mul_rows_kernel(const A* __restrict__ a, int lda, const int
 
 // ------------------------------------------------------------------ x += y / rms(y) * w
 // y float or A: [P][T][d] partial sums added in their order; a block per row, the row's y kept in shared memory.
+// With `out` (A, [gridDim.x][d]) the row's norm for the next reader follows in the same pass: out = x / rms(x) * w2 of
+// the stream as it now stands; `rows` (or null) picks the stream's rows that are worked on, out's rows stay in order.
 template <typename A>
 __global__ void add_rms_normed_kernel(float* __restrict__ x, const void* __restrict__ y, int y_f32, int P, int T,
-                                      const void* __restrict__ w, int w_f32, int d, float eps) {
+                                      const void* __restrict__ w, int w_f32, int d, float eps, const int* __restrict__ rows,
+                                      const void* __restrict__ w2, int w2_f32, float eps2, A* __restrict__ out) {
   extern __shared__ __align__(16) float rowbuf[];
   __shared__ float red[32];
-  int t = blockIdx.x;
+  int t = rows ? rows[blockIdx.x] : blockIdx.x;
   float ss = 0.f;
   for (int j = threadIdx.x; j < d; j += blockDim.x) {
     float v = 0.f;
@@ -379,16 +382,27 @@ __global__ void add_rms_normed_kernel(float* __restrict__ x, const void* __restr
     ss += v * v;
   }
   float r = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
-  for (int j = threadIdx.x; j < d; j += blockDim.x) x[(size_t)t * d + j] += rowbuf[j] * r * load_w(w, w_f32, j);
+  float ss2 = 0.f;
+  for (int j = threadIdx.x; j < d; j += blockDim.x) {
+    float v = x[(size_t)t * d + j] + rowbuf[j] * r * load_w(w, w_f32, j);
+    x[(size_t)t * d + j] = v;
+    rowbuf[j] = v;                             // a column is one thread's in every pass
+    ss2 += v * v;
+  }
+  if (!out) return;
+  float r2 = 1.0f / sqrtf(block_sum(ss2, red) / (float)d + eps2);
+  for (int j = threadIdx.x; j < d; j += blockDim.x)
+    out[(size_t)blockIdx.x * d + j] = from_f32<A>(rowbuf[j] * r2 * load_w(w2, w2_f32, j));
 }
 
 // four columns a thread (d a multiple of four); the partial sums are added in the same order
 template <typename A>
 __global__ void add_rms_normed_vec_kernel(float* __restrict__ x, const void* __restrict__ y, int y_f32, int P, int T,
-                                          const void* __restrict__ w, int w_f32, int d, float eps) {
+                                          const void* __restrict__ w, int w_f32, int d, float eps, const int* __restrict__ rows,
+                                          const void* __restrict__ w2, int w2_f32, float eps2, A* __restrict__ out) {
   extern __shared__ __align__(16) float rowbuf[];
   __shared__ float red[32];
-  int t = blockIdx.x;
+  int t = rows ? rows[blockIdx.x] : blockIdx.x;
   float ss = 0.f;
   for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -400,6 +414,7 @@ __global__ void add_rms_normed_vec_kernel(float* __restrict__ x, const void* __r
     ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
   }
   float r = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
+  float ss2 = 0.f;
   for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
     float4 v = *(const float4*)(rowbuf + j);
     float4 xv = *(const float4*)(x + (size_t)t * d + j);
@@ -408,6 +423,15 @@ __global__ void add_rms_normed_vec_kernel(float* __restrict__ x, const void* __r
     xv.z += v.z * r * load_w(w, w_f32, j + 2);
     xv.w += v.w * r * load_w(w, w_f32, j + 3);
     *(float4*)(x + (size_t)t * d + j) = xv;
+    *(float4*)(rowbuf + j) = xv;
+    ss2 += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
+  }
+  if (!out) return;
+  float r2 = 1.0f / sqrtf(block_sum(ss2, red) / (float)d + eps2);
+  for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+    float4 v = *(const float4*)(rowbuf + j);
+    st4(out + (size_t)blockIdx.x * d + j, make_float4(v.x * r2 * load_w(w2, w2_f32, j), v.y * r2 * load_w(w2, w2_f32, j + 1),
+                                                      v.z * r2 * load_w(w2, w2_f32, j + 2), v.w * r2 * load_w(w2, w2_f32, j + 3)));
   }
 }
 

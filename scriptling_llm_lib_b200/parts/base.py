@@ -29,7 +29,8 @@ Interfaces (duck-typed; the base classes document them):
                                               delta: None or either form of y
   PositionEncoding.prepare(max_positions, device); .rotation() or .transform(...)   see below
   StreamInput.forward(residual, delta, ctx)   reads the stream itself (after taking the pending addend in) and
-                                              the step's token ids, and adds to the stream in place
+                                              the step's token ids, and adds to the stream in place (or returns
+                                              what the next norm still has to add)
 
 A norm between two products can be folded into them (optional, and only where all three agree): a
 row's 1/rms is one number, so (v / rms * w) W^T = (1 / rms) * ((v * w) W^T). A norm that can be
@@ -150,9 +151,10 @@ class PositionEncoding(Part):
 class StreamInput(Part):
     """A part that is no sublayer on a norm's output: it reads the residual stream as it stands (the pending
     addend `delta` taken in first) together with what the step knows of its tokens (`ctx.token_ids`), and adds
-    its result to the stream in place. Nothing is left pending behind it."""
+    its result to the stream in place, or returns what is still to be added in a form that the layer's
+    arrangement hands to the next norm (None: nothing is pending)."""
 
-    def forward(self, residual, delta, ctx) -> None:
+    def forward(self, residual, delta, ctx):
         raise NotImplementedError
 
 

@@ -241,7 +241,7 @@ class PreNormInputBlock(Block):
     one, a stream input: a part that reads the stream as it stands and the step's tokens and adds to it. Roles:
     `mixer_norm`, `mixer`, both or neither of `feed_forward_norm`, `feed_forward`, and optionally `stream_input`.
     The mixer may keep per-sequence state (it is handed the unit's as `state=`); the norms are of the kind that
-    takes a plain pending addend (`rmsnorm`)."""
+    takes a plain pending addend or one that is still to be divided by its own root mean square (`rmsnorm`)."""
 
     def __init__(self, spec: LayerSpec):
         self.mixer_norm = NORMS.build(_role(spec, "mixer_norm"))
@@ -279,8 +279,7 @@ class PreNormInputBlock(Block):
             a = self._addend(self.feed_forward.forward(h2, ctx), ctx)
         if self.stream_input is None:
             return a
-        self.stream_input.forward(residual, a, ctx)
-        return None
+        return self.stream_input.forward(residual, a, ctx)
 
 
 ARRANGEMENTS.register("pre_norm", PreNormBlock)

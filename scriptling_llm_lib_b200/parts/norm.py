@@ -38,8 +38,24 @@ class RMSNorm(Norm):
             return delta
         n = residual.shape[0] if rows is None else rows.shape[0]
         y = torch.empty((n, self.width), dtype=ctx.dtype, device=residual.device)
+        if isinstance(delta, RmsNormedAddend):  # the addend's own norm, the sum and this norm in one pass
+            ctx.kernels.gate.add_rms_normed(residual, delta.y, delta.weight, delta.eps, norm=(self.weight, self.eps, y), rows=rows)
+            return y
         ctx.kernels.add_rmsnorm(residual, delta, rows, self.weight, y, self.eps)
         return y
+
+
+@dataclass
+class RmsNormedAddend:
+    """An addend that joins the residual stream divided by its own root mean square: x += y / sqrt(mean(y^2) + eps) * weight.
+    `y` is [T, width] (float32 or the engine's dtype) or float32 [P, T, width] partial sums, `weight` float32. The RMS norm
+    that reads the stream next does both in one pass; `apply` does the sum by itself for a reader that is none."""
+    y: Any
+    weight: Any
+    eps: float
+
+    def apply(self, residual, ctx) -> None:
+        ctx.kernels.gate.add_rms_normed(residual, self.y, self.weight, self.eps)
 
 
 class WeightedNorm(Norm):

@@ -7,6 +7,7 @@ the columns [i * dim, (i + 1) * dim)). With x the residual stream as it stands b
     y = Wproj g                       [width]
     x += y / sqrt(mean(y^2) + eps) * w
 
+The last line is left pending (`RmsNormedAddend`): the norm that reads the stream next does it in its own pass.
 The stream's sum and the norm are float32; the two products are the library's (in the engine's dtype on the
 stream rounded once, with float32 sums), the second one leaving float32. The table is one tensor for the
 model: the first layer that asks for it owns it in the weight list, the others name it as theirs (`owns_table`).
@@ -19,6 +20,7 @@ import torch
 from ..weights.spec import TensorSpec
 from .base import STREAM_INPUTS, StreamInput
 from .linear import Linear
+from .norm import RmsNormedAddend
 
 
 class TokenSideInput(StreamInput):
@@ -50,7 +52,7 @@ class TokenSideInput(StreamInput):
         if self.table.dtype != dtype:
             raise ValueError(f"the table {self.table_name} is {self.table.dtype}, the engine runs in {dtype}")
 
-    def forward(self, residual, delta, ctx) -> None:
+    def forward(self, residual, delta, ctx):
         k = ctx.kernels.gate
         T = residual.shape[0]
         xb = torch.empty((T, self.width), dtype=ctx.dtype, device=residual.device)
@@ -59,7 +61,7 @@ class TokenSideInput(StreamInput):
         g = torch.empty((T, self.dim), dtype=ctx.dtype, device=residual.device)
         k.gelu_mul_rows(a, ctx.token_ids, self.table, self.column, g)
         y = self.proj.forward(g, ctx, out_dtype=torch.float32, partials_ok=True)
-        k.add_rms_normed(residual, y, self.weight, self.eps)
+        return RmsNormedAddend(y, self.weight, self.eps)      # the next reader's norm adds it while it norms
 
 
 STREAM_INPUTS.register("token_side", TokenSideInput)

@@ -192,8 +192,10 @@ def test_the_residual_stream_after_every_layer(folders):
     delta = None
     for i, e in enumerate(eng.layout.schedule):
         delta = eng.model.blocks[e.layer].forward(x, delta, ctx, e.cache_unit, e.writes_cache)
-        assert delta is None                     # the token input leaves nothing pending
-        assert float((x.double().cpu() - want[i]).abs().max()) < 1e-4 * float(want[i].abs().max()), f"layer {i}"
+        full = x.clone()                         # the token input's addend is pending: the next norm adds it
+        assert delta is not None
+        delta.apply(full, ctx)
+        assert float((full.double().cpu() - want[i]).abs().max()) < 1e-4 * float(want[i].abs().max()), f"layer {i}"
     seq.close()
 
 
@@ -404,6 +406,21 @@ def test_the_small_kernels_against_their_formulas():
         xd = x.clone().cuda()
         ks.gate.add_rms_normed(xd, y.cuda(), w.cuda(), 1e-3)
         assert float((xd.cpu().double() - x.double() - plain.rms_norm(y.double().sum(0), w, 1e-3)).abs().max()) < 1e-5
+        # the same with the next norm's output in the pass, on all rows and on picked rows, at both widths
+        for xx, yy, ww in ((x, y, w), (torch.randn(6, 50, generator=g), torch.randn(3, 6, 50, generator=g), torch.randn(50, generator=g))):
+            w2 = (torch.rand(xx.shape[1], generator=g) + 0.5).to(dtype)
+            after = xx.double() + plain.rms_norm(yy.double().sum(0), ww, 1e-3)
+            normed = plain.rms_norm(after, w2.double(), 1e-2)
+            xd = xx.clone().cuda()
+            out = torch.empty(xx.shape, dtype=dtype, device="cuda")
+            ks.gate.add_rms_normed(xd, yy.cuda(), ww.cuda(), 1e-3, norm=(w2.cuda(), 1e-2, out))
+            assert float((xd.cpu().double() - after).abs().max()) < 1e-5
+            assert float((out.cpu().double() - normed).abs().max()) < tol * float(normed.abs().max())
+            pick = torch.tensor([4, 1], dtype=torch.int32)
+            xd = xx.clone().cuda()
+            out = torch.empty((2, xx.shape[1]), dtype=dtype, device="cuda")
+            ks.gate.add_rms_normed(xd, yy.cuda(), ww.cuda(), 1e-3, norm=(w2.cuda(), 1e-2, out), rows=pick.cuda())
+            assert float((out.cpu().double() - normed[pick.long()]).abs().max()) < tol * float(normed.abs().max())
         xd = x.clone().cuda()
         xb = torch.empty((5, 72), dtype=dtype, device="cuda")
         ks.gate.add_cast(xd, y.cuda(), xb)
