@@ -312,6 +312,21 @@ __global__ void head_gate_kernel(A* __restrict__ o, int ldo, const void* __restr
   *p = from_f32<A>(to_f32(*p) * s);
 }
 
+// eight neighbouring columns a thread: vd, ldo multiples of eight, o aligned for the wide access
+template <typename A>
+__global__ void head_gate_vec8_kernel(A* __restrict__ o, int ldo, const void* __restrict__ g, int g_f32, int ldg, int T, int H, int vd) {
+  size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  size_t wrow = (size_t)H * vd;
+  if (i >= (size_t)T * wrow) return;
+  int t = (int)(i / wrow), r = (int)(i % wrow);
+  float s = sigmoid_f(ld_flag<A>(g, g_f32, (size_t)t * ldg + r / vd));
+  A* p = o + (size_t)t * ldo + r;
+  F8 v = ld8(p);
+#pragma unroll
+  for (int k = 0; k < 8; k++) v.f[k] *= s;
+  st8(p, v);
+}
+
 // four neighbouring columns a thread: vd, ldo multiples of four, o aligned for the wide access
 template <typename A>
 __global__ void head_gate_vec_kernel(A* __restrict__ o, int ldo, const void* __restrict__ g, int g_f32, int ldg, int T, int H, int vd) {

@@ -394,12 +394,13 @@ def test_the_small_kernels_against_their_formulas():
         want = (o.double().view(7, 3, 5) * torch.sigmoid(lg.double())[:, :, None]).view(7, 15)
         assert float((od.cpu().double() - want).abs().max()) < tol
         # the same over widths that take the four-wide kernels
-        o = torch.randn(9, 4 * 8, generator=g).to(dtype)
-        lg = torch.randn(9, 4, generator=g).to(dtype)
-        od = o.clone().cuda()
-        ks.gate.head_gate(od, lg.cuda(), 4, 8)
-        want = (o.double().view(9, 4, 8) * torch.sigmoid(lg.double())[:, :, None]).view(9, 32)
-        assert float((od.cpu().double() - want).abs().max()) < tol
+        for hh, vv in ((4, 8), (2, 12)):     # eight and four columns a thread
+            o = torch.randn(9, hh * vv, generator=g).to(dtype)
+            lg = torch.randn(9, hh, generator=g).to(dtype)
+            od = o.clone().cuda()
+            ks.gate.head_gate(od, lg.cuda(), hh, vv)
+            want = (o.double().view(9, hh, vv) * torch.sigmoid(lg.double())[:, :, None]).view(9, hh * vv)
+            assert float((od.cpu().double() - want).abs().max()) < tol
         x = torch.randn(5, 72, generator=g)
         y = torch.randn(2, 5, 72, generator=g)
         w = torch.randn(72, generator=g)
