@@ -524,7 +524,7 @@ def belasun_config(z):
              "scale": z["dim"] ** -0.5, "vdim": z["vdim"]}
     moe = {"expert": {"ff": z["expert_ff"], "limit": 7.0}, "kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}}
     return {"architecture": "Belasun", "layers": [{"type": "attention", "mixer": mixer, "mlp": moe}] * z["layers"],
-            "logit_softcap": 30.0, "norm": {"eps": 1e-6}, "token_side": {"dim": z["side"]}, "vocab": DESIGN_VOCAB, "width": z["width"]}
+            "logit_softcap": 25.0, "norm": {"eps": 1e-6}, "token_side": {"dim": z["side"]}, "vocab": DESIGN_VOCAB, "width": z["width"]}
 
 
 DESIGNS = {"sozilix": (DESIGN_SIZES, sozilix_config, 3), "muvorax": (MUVORAX_SIZES, muvorax_config, 6),
@@ -1041,7 +1041,7 @@ def gate_kernels_alone(args):
         us = timed(lambda i: ks.add_rmsnorm(x32[i], ad, None, wnb, xb, 1e-6), n_sets)
         report(f"add_rmsnorm ({label})", T, us, nbytes=T * W * (4 + 4 + esz + esz), like="add_rms_normed, add_cast")
         lg = torch.randn(max(B, 1), DESIGN_VOCAB, device=dev)
-        us = timed(lambda i: ks.gate.softcap(lg, 30.0), 1)
+        us = timed(lambda i: ks.gate.softcap(lg, 25.0), 1)
         report(f"softcap {lg.shape[0]} x {DESIGN_VOCAB} ({label})", T, us, nbytes=2 * lg.numel() * 4)
     return 0
 
