@@ -95,6 +95,20 @@ class KernelSet:
                                       _ptr(out, torch.float32, "out"), c_int(T), c_int(d), c_int(table.shape[0]),
                                       _ptr(err_flag, torch.int32, "err"), _stream()), "embed_rows")
 
+    def embed_pair_rows(self, ids, ctx, table, pair_table, buckets, mul_prev, mul_cur, last, out, err_flag):
+        """out float32 [T, d] = table[ids[t]] + pair_table[(previous token * mul_prev + ids[t] * mul_cur) mod buckets], the
+        pair table's row `buckets` for a sequence's first token; `last` int32 [slots]: the sequences' last tokens (read, then set)."""
+        T, d = out.shape
+        if tuple(pair_table.shape) != (buckets + 1, d) or table.shape[1] != d or last.dim() != 1:
+            raise KernelError(f"embed_pair_rows shapes: table {tuple(table.shape)}, pair table {tuple(pair_table.shape)}, buckets {buckets}")
+        _check(self._fn("embed_pair_rows")(_ptr(ids, torch.int32, "ids"), _ptr(ctx.tok_pos, torch.int32, "tok_pos"),
+                                           _ptr(ctx.tok_seq, torch.int32, "tok_seq"), _ptr(ctx.seq_start, torch.int32, "seq_start"),
+                                           _ptr(ctx.slots, torch.int32, "slots"), _ptr(table, self.dtype, "table"),
+                                           _ptr(pair_table, self.dtype, "pair_table"), _ptr(out, torch.float32, "out"), c_int(T), c_int(d),
+                                           c_int(table.shape[0]), c_int(buckets), c_longlong(mul_prev), c_longlong(mul_cur),
+                                           _ptr(last, torch.int32, "last"), _ptr(err_flag, torch.int32, "err"), _stream()),
+               "embed_pair_rows")
+
     # ------------------------------------------------------------------ norm
     def add_rmsnorm(self, x, delta, rows, weight, y, eps):
         """x float32 [T,d] residual (+= delta when rows is None); y [n,d] normed output. delta: None,
@@ -159,18 +173,22 @@ class KernelSet:
 
     # ------------------------------------------------------------------ attention
     def attn_paged(self, q, out, seq_start, seq_pos0, block_table, kpages, vpages, n_seqs, max_new, n_heads, n_kv,
-                   head_dim, window, scale):
+                   head_dim, window, scale, softcap=None, sink=None):
+        """`softcap`: a score s becomes softcap * tanh(s / softcap) before the softmax; `sink` float32 [n_heads]:
+        exp(sink[h]) joins head h's denominator with no key and no value."""
         _check(self._fn("attn_paged")(_ptr(q, self.dtype, "q"), c_int(q.shape[1]), _ptr(out, self.dtype, "out"),
                                       _ptr(seq_start, torch.int32, "seq_start"), _ptr(seq_pos0, torch.int32, "seq_pos0"),
                                       _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]),
                                       _ptr(kpages, self.dtype, "kpages"), _ptr(vpages, self.dtype, "vpages"),
                                       c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(n_kv), c_int(head_dim),
-                                      c_int(window or 0), c_float(scale), _stream()), "attn_paged")
+                                      c_int(window or 0), c_float(scale), c_float(softcap or 0.0),
+                                      _ptr(sink, torch.float32, "sink"), _stream()), "attn_paged")
 
     def attn_decode_split(self, q, out, seq_pos0, block_table, kpages, vpages, part, n_seqs, n_heads, n_kv, head_dim,
-                          window, scale, n_split):
+                          window, scale, n_split, softcap=None, sink=None):
         """One query per sequence, each sequence's keys split over `n_split` blocks (then merged);
-        `part`: float32 scratch of n_seqs * n_heads * n_split * (head_dim + 2) elements, or None for one split."""
+        `part`: float32 scratch of n_seqs * n_heads * n_split * (head_dim + 2) elements, or None for one split.
+        `softcap`, `sink`: as for `attn_paged`; the sink joins once, where the splits are merged."""
         need = n_seqs * n_heads * n_split * (head_dim + 2) if n_split > 1 else 0
         if need and (part is None or part.numel() < need):
             raise KernelError(f"attn_decode_split scratch holds {0 if part is None else part.numel()} floats, needs {need}")
@@ -180,7 +198,8 @@ class KernelSet:
                                              _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]),
                                              _ptr(kpages, self.dtype, "kpages"), _ptr(vpages, self.dtype, "vpages"),
                                              _ptr(part, torch.float32, "part"), c_int(n_seqs), c_int(n_heads), c_int(n_kv),
-                                             c_int(head_dim), c_int(window or 0), c_float(scale), c_int(n_split), _stream()),
+                                             c_int(head_dim), c_int(window or 0), c_float(scale), c_int(n_split),
+                                             c_float(softcap or 0.0), _ptr(sink, torch.float32, "sink"), _stream()),
                "attn_decode_split")
 
     @staticmethod
@@ -353,10 +372,11 @@ class TensorCoreGemm:
         matrix tile_group[t] (int32 on the device, M / 128 entries): rows laid out so that no 128 hold two groups.
         rows_used: an int32 on the device (one element), how many of the M rows hold anything; the rest is not worked.
         `glu` = (limit, alpha): every matrix's N rows are tiles of 8 gate rows and their 8 up rows, and out [M, N / 2]
-        (bfloat16) receives the clamped gate of each pair of sums, g' * sigmoid(alpha g') * (u' + 1)."""
+        (bfloat16) receives the clamped gate of each pair of sums, g' * sigmoid(alpha g') * (u' + 1); a limit of 0 stands
+        for the gate without a clamp, silu(g) * u."""
         M, K = a.shape
         G, N = w.shape[0], w.shape[1]
-        if glu is not None and (act is not None or N % 16 or out.dtype != torch.bfloat16 or not glu[0] > 0):
+        if glu is not None and (act is not None or N % 16 or out.dtype != torch.bfloat16 or glu[0] < 0):
             raise KernelError(f"gemm_grouped with a gate: {N} stacked rows a matrix, out {out.dtype}, act {act}, limit {glu[0]}")
         if (w.dim() != 3 or w.shape[2] != K or tuple(out.shape) != (M, N // 2 if glu is not None else N)
                 or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16
@@ -367,7 +387,7 @@ class TensorCoreGemm:
         _check(fn(_ptr(a, torch.bfloat16, "a"), _ptr(w, torch.bfloat16, "w"), _ptr(out, None, "out"), c_int(M), c_int(N), c_int(K),
                   c_int(K), c_int(K), c_int(out.shape[1]), c_int(1 if out.dtype == torch.float32 else 0),
                   _ptr(tile_group, torch.int32, "tile_group"), c_int(G), c_int(self.ACTS[act]), _ptr(rows_used, torch.int32, "rows_used"),
-                  c_float(0.0 if glu is None else glu[0]), c_float(0.0 if glu is None else glu[1]),
+                  c_int(0 if glu is None else 1), c_float(0.0 if glu is None else glu[0]), c_float(0.0 if glu is None else glu[1]),
                   _ptr(err_flag, torch.int32, "err_flag"), _stream()), "gemm_grouped")
 
     def gemm_act(self, a, w, out, err_flag, act: str):
@@ -813,15 +833,16 @@ class MixKernels:
                                          c_int(o.shape[0]), c_int(o.shape[1]), c_float(eps), c_int(self.GATES[gate_act]), _stream()),
                "gated_row_rms")
 
-    def latent_store(self, q, n_heads, dim, dkv, norm_w, eps, cos_sin, rot, ctx, block_table, pages, rank, rot_dim):
-        """Rotates the last rot_dim dims of every query head of q [T, H (dim + rot_dim)] in place and, with
+    def latent_store(self, q, n_heads, dim, dkv, norm_w, eps, cos_sin, rot, ctx, block_table, pages, rank, rot_dim, half=False):
+        """Rotates the last rot_dim dims of every query head of q [T, H (dim + rot_dim)] in place (pairs of neighbours, or
+        with `half` dim i with dim i + rot / 2) and, with
         `pages`, stores [dkv[:rank] / rms * norm_w | rotated dkv[rank:]] at the rows' places. q and dkv may be
         column slices of one buffer."""
         _check(self._fn("latent_store")(
             self._view(q, "q"), c_int(q.stride(0)), c_int(n_heads), c_int(dim),
             self._view(dkv, "dkv") if dkv is not None else c_void_p(0), c_int(dkv.stride(0) if dkv is not None else 0),
             _ptr(norm_w, torch.float32, "norm weight"), c_int(1), c_float(eps),
-            _ptr(cos_sin, torch.float32, "cos_sin"), c_int(rot), _ptr(ctx.tok_pos, torch.int32, "tok_pos"),
+            _ptr(cos_sin, torch.float32, "cos_sin"), c_int(rot), c_int(1 if half else 0), _ptr(ctx.tok_pos, torch.int32, "tok_pos"),
             _ptr(ctx.tok_seq, torch.int32, "tok_seq"), _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]),
             _ptr(pages, self.dtype if pages is not None else None, "pages"), c_int(q.shape[0]), c_int(rank), c_int(rot_dim),
             _stream()), "latent_store")
@@ -882,14 +903,19 @@ class MixKernels:
             _ptr(ctx.slots, torch.int32, "slots"), self._view(out, "out"), c_int(out.stride(0)), c_int(ctx.n_seqs),
             c_int(max(1, ctx.max_new)), c_int(inner), c_int(n_state), _stream()), "selective_scan")
 
-    def moe_route(self, z, correction, idx, wgt, n_groups, keep, top, scale, top_softmax=False):
+    ROUTERS = {"grouped_sigmoid": 0, "top_softmax": 1, "grouped_softmax": 2}
+
+    def moe_route(self, z, correction, idx, wgt, n_groups, keep, top, scale, top_softmax=False, router=None):
         """z float32 [T, E] the router's logits -> idx int32 [T, top] the chosen experts, wgt float32 [T, top] their weights.
         `top_softmax`: the highest z + correction (a bias; may be None) are chosen and weigh with the softmax over the
-        chosen ones alone; else sigmoid scores, a correction that only enters the picking, runs of experts."""
+        chosen ones alone; "grouped_softmax": scores are the softmax over all experts, a run of experts is rated by its best
+        score, the best open experts weigh with their scores as they are (times scale); else sigmoid scores, a correction
+        that only enters the picking, runs of experts rated by their best two."""
         T, E = z.shape
+        mode = self.ROUTERS[router] if router is not None else (1 if top_softmax else 0)
         _check(self._fn("moe_route")(_ptr(z, torch.float32, "z"), _ptr(correction, torch.float32, "correction"), c_int(1),
                                      _ptr(idx, torch.int32, "idx"), _ptr(wgt, torch.float32, "wgt"), c_int(T), c_int(E),
-                                     c_int(n_groups), c_int(keep), c_int(top), c_float(scale), c_int(1 if top_softmax else 0),
+                                     c_int(n_groups), c_int(keep), c_int(top), c_float(scale), c_int(mode),
                                      _stream()), "moe_route")
 
     def moe_pairs(self, h, wup, wdown, idx, wgt, hid, out, glu=None, tiled=False):
@@ -1036,6 +1062,22 @@ class GateKernels:
                                     c_int(self._flag(delta, "delta") if delta is not None else 0), c_int(P),
                                     _ptr(xb, self.dtype, "xb"), ctypes.c_longlong(x.numel()), _stream()), "add_cast")
 
+    def add_list_cast(self, x, addends, xb=None, vec=None):
+        """x float32 [T, d] += every tensor of `addends` ([T, d] float32 or element type, or float32 [P, T, d] partial sums, added
+        in their order) and `vec` (float32 [d], on every row); xb (element type [T, d], optional) = the stream rounded."""
+        if len(addends) > 8:
+            raise KernelError(f"{len(addends)} addends at once; the kernel takes 8")
+        for a in addends:
+            if tuple(a.shape[-2:]) != tuple(x.shape) or not a.is_contiguous() or not a.is_cuda or a.dim() not in (2, 3):
+                raise KernelError(f"addend {tuple(a.shape)} does not fit the stream {tuple(x.shape)}")
+        n = len(addends)
+        ptrs = (c_void_p * max(n, 1))(*[a.data_ptr() for a in addends])
+        f32 = (c_int * max(n, 1))(*[self._flag(a, "addend") for a in addends])
+        parts = (c_int * max(n, 1))(*[a.shape[0] if a.dim() == 3 else 1 for a in addends])
+        _check(self._fn("add_list_cast")(_ptr(x, torch.float32, "x"), ptrs, f32, parts, c_int(n), _ptr(vec, torch.float32, "vec"),
+                                         c_int(x.shape[1]), _ptr(xb, self.dtype if xb is not None else None, "xb"),
+                                         ctypes.c_longlong(x.numel()), _stream()), "add_list_cast")
+
     def gelu_mul_rows(self, a, ids, table, col0, out):
         """out [T, D] = gelu_tanh(a [T, D]) * table[ids[t], col0 : col0 + D]."""
         _check(self._fn("gelu_mul_rows")(self._view(a, "a"), c_int(a.stride(0)), _ptr(ids, torch.int32, "ids"),
@@ -1043,13 +1085,25 @@ class GateKernels:
                                          _ptr(out, self.dtype, "out"), c_int(a.shape[0]), c_int(a.shape[1]), _stream()),
                "gelu_mul_rows")
 
-    def add_rms_normed(self, x, y, weight, eps, norm=None, rows=None):
+    def add_rms_normed(self, x, y, weight, eps, norm=None, rows=None, vec=None, dyt=None):
         """x float32 [T, d] += y / sqrt(mean(y^2) + eps) * weight; y [T, d] or [P, T, d] partial sums (float32 or element type).
         `norm` = (weight2, eps2, out): in the same pass out (element type) = x / sqrt(mean(x^2) + eps2) * weight2 of the
-        stream as it then stands; with `rows` (int32 on the device) only those rows are worked on and out has a row for each."""
+        stream as it then stands; with `rows` (int32 on the device) only those rows are worked on and out has a row for each.
+        `dyt` = (weight2, bias2, alpha2, out), all float32: the norm that follows is tanh(alpha2 x) * weight2 + bias2 instead.
+        `vec` (float32 [d]): added to every row worked on, with the addend."""
         P = y.shape[0] if y.dim() == 3 else 1
+        b2, alpha2 = None, 0.0
+        if dyt is not None:
+            if norm is not None:
+                raise KernelError("one norm follows the sum, not two")
+            w2, b2, alpha2, out = dyt
+            norm = (w2, 0.0, out)
+            if w2.dtype != torch.float32 or b2.dtype != torch.float32 or b2.shape[0] != x.shape[1]:
+                raise KernelError("the norm without statistics takes float32 weight and bias of the stream's width")
         if tuple(y.shape[-2:]) != tuple(x.shape) or not y.is_contiguous() or (rows is not None and norm is None):
             raise KernelError(f"y {tuple(y.shape)} does not fit the stream {tuple(x.shape)}")
+        if vec is not None and (vec.dtype != torch.float32 or vec.numel() != x.shape[1]):
+            raise KernelError(f"the row vector {tuple(vec.shape)} {vec.dtype} does not fit the stream {tuple(x.shape)}")
         w2, eps2, out = norm if norm is not None else (None, 0.0, None)
         n_out = 0 if norm is None else (x.shape[0] if rows is None else rows.shape[0])
         if norm is not None and (tuple(out.shape) != (n_out, x.shape[1]) or not out.is_contiguous() or w2.shape[0] != x.shape[1]):
@@ -1058,12 +1112,14 @@ class GateKernels:
                                           c_int(x.shape[0]), _ptr(weight, None, "weight"), c_int(self._flag(weight, "weight")),
                                           c_int(x.shape[1]), c_float(eps), _ptr(rows, torch.int32, "rows"), c_int(n_out),
                                           _ptr(w2, None, "weight2"), c_int(self._flag(w2, "weight2") if w2 is not None else 0),
-                                          c_float(eps2), _ptr(out, self.dtype if out is not None else None, "out"), _stream()),
+                                          c_float(eps2), _ptr(out, self.dtype if out is not None else None, "out"),
+                                          _ptr(vec, torch.float32, "vec"), _ptr(b2, torch.float32, "bias2"), c_float(alpha2), _stream()),
                "add_rms_normed")
 
-    def softcap(self, x, cap):
-        """x float32 = cap * tanh(x / cap), in place."""
-        _check(self._fn("softcap")(_ptr(x, torch.float32, "x"), ctypes.c_longlong(x.numel()), c_float(cap), _stream()), "softcap")
+    def softcap(self, x, cap, scale=1.0):
+        """x float32 = cap * tanh(x * scale / cap), in place; without a cap (None or 0), x * scale."""
+        _check(self._fn("softcap")(_ptr(x, torch.float32, "x"), ctypes.c_longlong(x.numel()), c_float(cap or 0.0), c_float(scale),
+                                   _stream()), "softcap")
 
 
 class CastKernels:

@@ -366,6 +366,44 @@ __global__ void add_cast_vec_kernel(float* __restrict__ x, const void* __restric
   st4(xb + i, v);
 }
 
+// several addends at once: x float [T][d] += sum over the list's entries k, each [P_k][T][d] partial sums (float or A) added in
+// their order, and + vec[j] (float [d], or null) on every row; xb (A, or null) = the rounded stream. One pass over the stream.
+#define GATE_MAX_ADDENDS 8
+struct AddList {
+  const void* p[GATE_MAX_ADDENDS];
+  int f32[GATE_MAX_ADDENDS];
+  int P[GATE_MAX_ADDENDS];
+  int count;
+};
+template <typename A>
+__global__ void add_list_cast_kernel(float* __restrict__ x, AddList l, const float* __restrict__ vec, int d, A* __restrict__ xb, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = x[i];
+  for (int k = 0; k < l.count; k++)
+    for (int q = 0; q < l.P[k]; q++) v += ld_flag<A>(l.p[k], l.f32[k], (size_t)q * n + i);
+  if (vec) v += vec[i % d];
+  x[i] = v;
+  if (xb) xb[i] = from_f32<A>(v);
+}
+template <typename A>
+__global__ void add_list_cast_vec_kernel(float* __restrict__ x, AddList l, const float* __restrict__ vec, int d, A* __restrict__ xb, size_t n) {
+  size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  float4 v = *(const float4*)(x + i);
+  for (int k = 0; k < l.count; k++)
+    for (int q = 0; q < l.P[k]; q++) {
+      float4 a = ld4f<A>(l.p[k], l.f32[k], (size_t)q * n + i);
+      v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+    }
+  if (vec) {
+    float4 b = *(const float4*)(vec + i % d);
+    v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+  }
+  *(float4*)(x + i) = v;
+  if (xb) st4(xb + i, v);
+}
+
 // ------------------------------------------------------------------ gelu(a) * a slice of the token's table row
 // out[t][j] = gelu_tanh(a[t][j]) * table[ids[t]][col0 + j], j < D; table [rows][ldt] of A.
 template <typename A>
@@ -381,11 +419,14 @@ __global__ void gelu_mul_rows_kernel(const A* __restrict__ a, int lda, const int
 // ------------------------------------------------------------------ x += y / rms(y) * w
 // y float or A: [P][T][d] partial sums added in their order; a block per row, the row's y kept in shared memory.
 // With `out` (A, [gridDim.x][d]) the row's norm for the next reader follows in the same pass: out = x / rms(x) * w2 of
-// the stream as it now stands; `rows` (or null) picks the stream's rows that are worked on, out's rows stay in order.
+// the stream as it now stands, or with `b2` the norm without statistics tanh(alpha2 x) * w2 + b2 (w2, b2 float then);
+// `rows` (or null) picks the stream's rows that are worked on, out's rows stay in order. `vec` (float [d], or null)
+// is added to the row as well.
 template <typename A>
 __global__ void add_rms_normed_kernel(float* __restrict__ x, const void* __restrict__ y, int y_f32, int P, int T,
                                       const void* __restrict__ w, int w_f32, int d, float eps, const int* __restrict__ rows,
-                                      const void* __restrict__ w2, int w2_f32, float eps2, A* __restrict__ out) {
+                                      const void* __restrict__ w2, int w2_f32, float eps2, A* __restrict__ out,
+                                      const float* __restrict__ vec, const float* __restrict__ b2, float alpha2) {
   extern __shared__ __align__(16) float rowbuf[];
   __shared__ float red[32];
   int t = rows ? rows[blockIdx.x] : blockIdx.x;
@@ -400,11 +441,17 @@ __global__ void add_rms_normed_kernel(float* __restrict__ x, const void* __restr
   float ss2 = 0.f;
   for (int j = threadIdx.x; j < d; j += blockDim.x) {
     float v = x[(size_t)t * d + j] + rowbuf[j] * r * load_w(w, w_f32, j);
+    if (vec) v += vec[j];
     x[(size_t)t * d + j] = v;
     rowbuf[j] = v;                             // a column is one thread's in every pass
     ss2 += v * v;
   }
   if (!out) return;
+  if (b2) {
+    for (int j = threadIdx.x; j < d; j += blockDim.x)
+      out[(size_t)blockIdx.x * d + j] = from_f32<A>(tanhf(alpha2 * rowbuf[j]) * load_w(w2, 1, j) + b2[j]);
+    return;
+  }
   float r2 = 1.0f / sqrtf(block_sum(ss2, red) / (float)d + eps2);
   for (int j = threadIdx.x; j < d; j += blockDim.x)
     out[(size_t)blockIdx.x * d + j] = from_f32<A>(rowbuf[j] * r2 * load_w(w2, w2_f32, j));
@@ -414,7 +461,8 @@ __global__ void add_rms_normed_kernel(float* __restrict__ x, const void* __restr
 template <typename A>
 __global__ void add_rms_normed_vec_kernel(float* __restrict__ x, const void* __restrict__ y, int y_f32, int P, int T,
                                           const void* __restrict__ w, int w_f32, int d, float eps, const int* __restrict__ rows,
-                                          const void* __restrict__ w2, int w2_f32, float eps2, A* __restrict__ out) {
+                                          const void* __restrict__ w2, int w2_f32, float eps2, A* __restrict__ out,
+                                          const float* __restrict__ vec, const float* __restrict__ b2, float alpha2) {
   extern __shared__ __align__(16) float rowbuf[];
   __shared__ float red[32];
   int t = rows ? rows[blockIdx.x] : blockIdx.x;
@@ -437,11 +485,24 @@ __global__ void add_rms_normed_vec_kernel(float* __restrict__ x, const void* __r
     xv.y += v.y * r * load_w(w, w_f32, j + 1);
     xv.z += v.z * r * load_w(w, w_f32, j + 2);
     xv.w += v.w * r * load_w(w, w_f32, j + 3);
+    if (vec) {
+      float4 b = *(const float4*)(vec + j);
+      xv.x += b.x; xv.y += b.y; xv.z += b.z; xv.w += b.w;
+    }
     *(float4*)(x + (size_t)t * d + j) = xv;
     *(float4*)(rowbuf + j) = xv;
     ss2 += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
   }
   if (!out) return;
+  if (b2) {
+    for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+      float4 v = *(const float4*)(rowbuf + j);
+      float4 ww = *(const float4*)((const float*)w2 + j), bb = *(const float4*)(b2 + j);
+      st4(out + (size_t)blockIdx.x * d + j, make_float4(tanhf(alpha2 * v.x) * ww.x + bb.x, tanhf(alpha2 * v.y) * ww.y + bb.y,
+                                                        tanhf(alpha2 * v.z) * ww.z + bb.z, tanhf(alpha2 * v.w) * ww.w + bb.w));
+    }
+    return;
+  }
   float r2 = 1.0f / sqrtf(block_sum(ss2, red) / (float)d + eps2);
   for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
     float4 v = *(const float4*)(rowbuf + j);
@@ -450,10 +511,12 @@ __global__ void add_rms_normed_vec_kernel(float* __restrict__ x, const void* __r
   }
 }
 
-// ------------------------------------------------------------------ cap * tanh(x / cap)
-__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+// ------------------------------------------------------------------ cap * tanh(x * scale / cap) (cap <= 0: x * scale)
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap, float scale) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) x[i] = cap * tanhf(x[i] / cap);
+  if (i >= n) return;
+  float v = x[i] * scale;
+  x[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
 }
 
 }  // namespace gate

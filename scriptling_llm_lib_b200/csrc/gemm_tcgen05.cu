@@ -737,11 +737,11 @@ SLLM_EXPORT int sllm_gemm_tc_fold_bf16(const void* A, const void* B, void* C, in
 // 0 .. n_groups - 1). The caller lays the rows of A out so that no tile holds rows of two groups. The one-SM kernel
 // (tiles of 128 rows); a tile's columns beyond N read the next group's rows and are not written. m_used (or null): an
 // int on the device, the rows of A in use; the tiles behind them are left alone (their number is known on the device only).
-// glu_limit > 0 (act 0, bfloat16 out, N a multiple of 16): every matrix's rows come in tiles of 16 (8 gate rows, 8 up
-// rows) and C[M, N/2] receives the clamped gate of each pair (see TcFold).
+// gated (act 0, bfloat16 out, N a multiple of 16): every matrix's rows come in tiles of 16 (8 gate rows, 8 up
+// rows) and C[M, N/2] receives the gate of each pair: the clamped one with glu_limit > 0 (see TcFold), else silu(g) * u.
 SLLM_EXPORT int sllm_gemm_tc_grouped_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                                           int out_f32, const int* tile_group, int n_groups, int act, const int* m_used,
-                                          float glu_limit, float glu_alpha, int* err, cudaStream_t stream) {
+                                          int gated, float glu_limit, float glu_alpha, int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (lda & 7) || (ldb & 7) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || !tile_group || n_groups < 1)
     return SLLM_ERR_ARG;
@@ -759,9 +759,9 @@ SLLM_EXPORT int sllm_gemm_tc_grouped_bf16(const void* A, const void* B, void* C,
   if (rc) return rc;
   rc = tc_make_map(&mb, B, n_groups * N, K, ldb, big ? 256 : 128);
   if (rc) return rc;
-  if (glu_limit > 0.f) {
+  if (gated) {
     if (act || out_f32 || (N & 15)) return SLLM_ERR_ARG;
-    fd.glu_limit = glu_limit;
+    fd.glu_limit = glu_limit > 0.f ? glu_limit : 0.f;
     fd.glu_alpha = glu_alpha;
     return big ? tc_launch<256, 4, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp, fd)
                : tc_launch<128, 6, TC_EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, 0, err, stream, rp, fd);

@@ -28,6 +28,41 @@ __global__ void embed_rows_kernel(const int* __restrict__ ids, const W* __restri
   for (int j = threadIdx.x; j < d; j += blockDim.x) dst[j] = ok ? to_f32(src[j]) : 0.f;
 }
 
+// The embedding with a second table looked up by the pair (previous token, token):
+// out[t, :] = table[ids[t], :] + pair_table[r, :], r = (prev * mul_prev + ids[t] * mul_cur) mod buckets, and r = buckets (the
+// table's last row) for a sequence's first token (tok_pos 0). The previous token of a step's row is the row before it; for
+// the first row of a sequence's run it is what `last` [slots] holds, the sequence's state, which the same block then sets to
+// the run's last token (one block reads and writes a sequence's entry, so runs of any length keep it in order).
+template <typename W>
+__global__ void embed_pair_rows_kernel(const int* __restrict__ ids, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                       const int* __restrict__ seq_start, const int* __restrict__ slots, const W* __restrict__ table,
+                                       const W* __restrict__ pair_table, float* __restrict__ out, int d, int vocab, int buckets,
+                                       long long mul_prev, long long mul_cur, int* __restrict__ last, int* err) {
+  __shared__ int s_prev;
+  int t = blockIdx.x;
+  int id = ids[t];
+  int b = tok_seq[t], first = seq_start[b];
+  if (threadIdx.x == 0) {
+    int prev = 0;
+    if (t > first) prev = ids[t - 1];
+    else {
+      int slot = slots[b];
+      prev = last[slot];
+      last[slot] = ids[seq_start[b + 1] - 1];
+    }
+    s_prev = prev;
+  }
+  __syncthreads();
+  int prev = s_prev;
+  bool ok = id >= 0 && id < vocab && prev >= 0 && prev < vocab;
+  if (!ok && threadIdx.x == 0) atomicExch(err, 1);
+  long long r = tok_pos[t] == 0 ? (long long)buckets : ((long long)prev * mul_prev + (long long)id * mul_cur) % (long long)buckets;
+  const W* src = table + (size_t)(ok ? id : 0) * d;
+  const W* src2 = pair_table + (size_t)(ok ? r : 0) * d;
+  float* dst = out + (size_t)t * d;
+  for (int j = threadIdx.x; j < d; j += blockDim.x) dst[j] = ok ? to_f32(src[j]) + to_f32(src2[j]) : 0.f;
+}
+
 // ------------------------------------------------------------------ residual add + RMSNorm
 // v = x[row] + delta[row]; y = (v * 1/sqrt(mean(v^2) + eps)) * w.
 // delta is either one array of the element type (n_parts == 0) or n_parts float arrays
@@ -502,6 +537,13 @@ __global__ void rope_kv_write_vec_kernel(A* __restrict__ qkv, int ld, const int*
 #define ATT_BK 32
 #define ATT_THREADS 128
 
+// A capped score, and a softmax denominator l (relative to the maximum m) that a sink has joined: the sink counts
+// once, exp(sink - m), whatever the number of keys; with nothing seen yet the sink alone makes the denominator 1.
+__device__ __forceinline__ float capped(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+__device__ __forceinline__ float sink_joined(float l, float m, float sink) {
+  return m == -INFINITY ? 1.0f : l + expf(sink - m);
+}
+
 struct AttnArgs {
   const void* q;        // [T, q_ld] rotated queries; head h at columns h*hd
   int q_ld;
@@ -514,6 +556,8 @@ struct AttnArgs {
   const void* vpages;
   int H, G, hd, window;
   float scale;
+  float softcap;        // > 0: a score s becomes softcap * tanh(s / softcap) before the softmax
+  const float* sink;    // [H] or null: exp(sink[h]) joins the softmax's denominator, with no key and no value
 };
 
 template <typename A, int NACC>
@@ -577,6 +621,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_paged_kernel(AttnArgs p) {
       float dot = 0.f;
       for (int dd = 0; dd < hd; dd++) dot = fmaf(qv[dd], kv[dd], dot);
       float s = dot * p.scale;
+      if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
       bool seen = page >= 0 && kpos <= qpos && kpos >= first_seen(qpos, p.window);
       if (!seen) s = -INFINITY;
       float m_new = fmaxf(m[i], warp_max(s));
@@ -602,6 +647,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_paged_kernel(AttnArgs p) {
   for (int i = 0; i < QPW; i++) {
     int qi = warp * QPW + i;
     if (qi >= nq) continue;
+    if (p.sink) l[i] = sink_joined(l[i], m[i], p.sink[h]);
     float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
 #pragma unroll
     for (int a = 0; a < NACC; a++) {
@@ -708,7 +754,7 @@ __global__ void __launch_bounds__(256) attn_paged_tiled_kernel(AttnArgs p) {
       for (int j = 0; j < 4; j++) {
         int kpos = kt + tx * 4 + j;
         bool seen = page >= 0 && qi < nq && kpos <= qpos && kpos >= first_seen(qpos, p.window);
-        s[i][j] = seen ? s[i][j] * p.scale : -INFINITY;
+        s[i][j] = seen ? capped(s[i][j] * p.scale, p.softcap) : -INFINITY;
         mx = fmaxf(mx, s[i][j]);
       }
 #pragma unroll
@@ -764,6 +810,7 @@ __global__ void __launch_bounds__(256) attn_paged_tiled_kernel(AttnArgs p) {
 #pragma unroll
     for (int off = 1; off < 16; off <<= 1) ls += __shfl_xor_sync(0xffffffffu, ls, off);
     if (qi >= nq) continue;
+    if (p.sink) ls = sink_joined(ls, m[i], p.sink[h]);
     const float inv = ls > 0.f ? 1.0f / ls : 0.f;
 #pragma unroll
     for (int gg = 0; gg < NG; gg++) {
@@ -794,6 +841,8 @@ struct AttnSplitArgs {
   float* part;
   int H, G, hd, window, n_split;
   float scale;
+  float softcap;        // as in AttnArgs
+  const float* sink;
 };
 #define ATT_LOG2E 1.4426950408889634f
 
@@ -829,7 +878,7 @@ __global__ void __launch_bounds__(128) attn_decode_split_generic_kernel(AttnSpli
       for (int v = 0; v < NV; v++) {
         int d = dl + v * LPK * 4;
         float4 t = d < hd ? ld4(qrow + d) : make_float4(0.f, 0.f, 0.f, 0.f);
-        const float sc = p.scale * ATT_LOG2E;
+        const float sc = p.softcap > 0.f ? p.scale : p.scale * ATT_LOG2E;   // a capped score is brought to base 2 after the cap
         qv[r][v][0] = t.x * sc; qv[r][v][1] = t.y * sc; qv[r][v][2] = t.z * sc; qv[r][v][3] = t.w * sc;
         acc[r][v][0] = acc[r][v][1] = acc[r][v][2] = acc[r][v][3] = 0.f;
       }
@@ -866,6 +915,7 @@ __global__ void __launch_bounds__(128) attn_decode_split_generic_kernel(AttnSpli
           }
 #pragma unroll
           for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+          if (p.softcap > 0.f) d = p.softcap * ATT_LOG2E * tanhf(d / p.softcap);
           s[u] = ok[u] ? d : -INFINITY;
           m_new = fmaxf(m_new, s[u]);
         }
@@ -930,6 +980,7 @@ __global__ void __launch_bounds__(128) attn_decode_split_generic_kernel(AttnSpli
         ls += sm_ml[(w * NREP + r) * 2 + 1] * cw;
       }
       if (p.n_split == 1) {
+        if (p.sink) ls = mn == -INFINITY ? 1.0f : ls + exp2f(p.sink[h] * ATT_LOG2E - mn);
         ((A*)p.out)[((size_t)b * p.H + h) * hd + dd] = from_f32<A>(ls > 0.f ? a / ls : 0.f);
       } else {
         float* dst = p.part + (((size_t)b * p.H + h) * p.n_split + split) * (hd + 2);
@@ -941,9 +992,10 @@ __global__ void __launch_bounds__(128) attn_decode_split_generic_kernel(AttnSpli
   }
 }
 
-// out[b, h*hd + d] = sum_s acc_s[d] 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits added in order
+// out[b, h*hd + d] = sum_s acc_s[d] 2^(m_s - M) / (sum_s l_s 2^(m_s - M) [+ 2^(sink_h log2 e - M)]), splits added in order
 template <typename A>
-__global__ void attn_split_merge_kernel(const float* __restrict__ part, A* __restrict__ out, int H, int hd, int n_split) {
+__global__ void attn_split_merge_kernel(const float* __restrict__ part, A* __restrict__ out, int H, int hd, int n_split,
+                                        const float* __restrict__ sink) {
   const int h = blockIdx.x, b = blockIdx.y;
   const float* src = part + ((size_t)b * H + h) * n_split * (hd + 2);
   float mn = -INFINITY;
@@ -956,6 +1008,7 @@ __global__ void attn_split_merge_kernel(const float* __restrict__ part, A* __res
       a += ps[dd] * c;
       ls += ps[hd + 1] * c;
     }
+    if (sink) ls = mn == -INFINITY ? 1.0f : ls + exp2f(sink[h] * ATT_LOG2E - mn);     // the sink counts once, here
     out[((size_t)b * H + h) * hd + dd] = from_f32<A>(ls > 0.f ? a / ls : 0.f);
   }
 }

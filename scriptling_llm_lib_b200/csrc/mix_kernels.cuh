@@ -396,19 +396,22 @@ __global__ void gated_row_rms_kernel(const float* __restrict__ o, const A* __res
 template <typename A>
 __global__ void latent_store_kernel(A* __restrict__ q, int ldq, int H, int D, const A* __restrict__ dkv, int ldk,
                                     const void* __restrict__ nw, int nw_f32, float eps, const float2* __restrict__ cos_sin,
-                                    int rot, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                    int rot, int half, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                     const int* __restrict__ block_table, int max_pages, A* __restrict__ pages, int R, int P) {
   __shared__ float red[32];
   int t = blockIdx.x;
   int pos = tok_pos[t];
-  const float2* cs = cos_sin + (size_t)pos * (rot / 2);
-  for (int i = threadIdx.x; i < H * (rot / 2); i += blockDim.x) {
-    int h = i / (rot / 2), pr = i % (rot / 2);
-    A* qp = q + (size_t)t * ldq + (size_t)h * (D + P) + D + 2 * pr;
-    float u = to_f32(qp[0]), v = to_f32(qp[1]);
+  const int hr = rot / 2;
+  const float2* cs = cos_sin + (size_t)pos * hr;
+  // pair pr of the rotated part: dims (2 pr, 2 pr + 1), or with `half` dims (pr, pr + rot / 2)
+  for (int i = threadIdx.x; i < H * hr; i += blockDim.x) {
+    int h = i / hr, pr = i % hr;
+    A* qp = q + (size_t)t * ldq + (size_t)h * (D + P) + D;
+    int a = half ? pr : 2 * pr, b = half ? pr + hr : 2 * pr + 1;
+    float u = to_f32(qp[a]), v = to_f32(qp[b]);
     float2 c = cs[pr];
-    qp[0] = from_f32<A>(u * c.x - v * c.y);
-    qp[1] = from_f32<A>(v * c.x + u * c.y);
+    qp[a] = from_f32<A>(u * c.x - v * c.y);
+    qp[b] = from_f32<A>(v * c.x + u * c.y);
   }
   if (!pages) return;
   const A* row = dkv + (size_t)t * ldk;
@@ -422,17 +425,14 @@ __global__ void latent_store_kernel(A* __restrict__ q, int ldq, int H, int D, co
   int page = block_table[(size_t)tok_seq[t] * max_pages + pos / SLLM_PAGE];
   A* dst = pages + ((size_t)page * SLLM_PAGE + pos % SLLM_PAGE) * (R + P);
   for (int j = threadIdx.x; j < R; j += blockDim.x) dst[j] = from_f32<A>(to_f32(row[j]) * inv * load_w(nw, nw_f32, j));
-  for (int pr = threadIdx.x; pr < P / 2 + (P & 1); pr += blockDim.x) {
-    if (2 * pr + 1 < P && pr < rot / 2) {
-      float u = to_f32(row[R + 2 * pr]), v = to_f32(row[R + 2 * pr + 1]);
-      float2 c = cs[pr];
-      dst[R + 2 * pr] = from_f32<A>(u * c.x - v * c.y);
-      dst[R + 2 * pr + 1] = from_f32<A>(v * c.x + u * c.y);
-    } else {
-      dst[R + 2 * pr] = row[R + 2 * pr];
-      if (2 * pr + 1 < P) dst[R + 2 * pr + 1] = row[R + 2 * pr + 1];
-    }
+  for (int pr = threadIdx.x; pr < hr; pr += blockDim.x) {
+    int a = R + (half ? pr : 2 * pr), b = R + (half ? pr + hr : 2 * pr + 1);
+    float u = to_f32(row[a]), v = to_f32(row[b]);
+    float2 c = cs[pr];
+    dst[a] = from_f32<A>(u * c.x - v * c.y);
+    dst[b] = from_f32<A>(v * c.x + u * c.y);
   }
+  for (int j = 2 * hr + threadIdx.x; j < P; j += blockDim.x) dst[R + j] = row[R + j];
 }
 
 // gather: the cached vectors of a step's rows side by side, dense[t] = pages[place of (sequence, position) of row t].
@@ -912,6 +912,8 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(ScanArgs p) {
 
 // ------------------------------------------------------------------ routed experts
 // router: a warp per token. z [T][E] float32 are the router's logits (a product of the library, float32 sums).
+// mode 2: s = softmax(z + bias) over all experts; runs of experts as in mode 0 but a run is rated by its best s alone; the
+// `top` open experts with the highest s are picked and count with s * scale as it is (not renormalised).
 // mode 1: c = z + bias (corr; may be null), the `top` experts with the highest c are picked and count with the
 // softmax over the picked c alone (n_groups 1, scale unused). mode 0:
 // s = sigmoid(z), c = s + correction. The experts are cut into n_groups runs of equal length, a run is rated by its best
@@ -937,6 +939,23 @@ __global__ void __launch_bounds__(32 * MIX_ROUTE_WARPS) moe_route_kernel(const f
     ch[e] = mode ? sg : sg + load_w(corr, corr_f32, e);
   }
   __syncwarp();
+  if (mode == 2) {          // the scores are the softmax of z + bias over ALL experts; they rate and weigh
+    float mx = -INFINITY, sum = 0.f;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    for (int e = lane; e < E; e += 32) {
+      float ex = expf(s[e] - mx);
+      s[e] = ex;
+      sum += ex;
+    }
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) {
+      s[e] *= inv;
+      ch[e] = s[e];
+    }
+    __syncwarp();
+  }
   int gsz = E / n_groups;
   if (n_groups > 1) {
     for (int g = lane; g < n_groups; g += 32) {
@@ -946,7 +965,7 @@ __global__ void __launch_bounds__(32 * MIX_ROUTE_WARPS) moe_route_kernel(const f
         if (v > a) { b2 = a; a = v; }
         else if (v > b2) b2 = v;
       }
-      gs[g] = gsz > 1 ? a + b2 : a;
+      gs[g] = (gsz > 1 && mode != 2) ? a + b2 : a;       // mode 2 rates a run by its best member alone
     }
     __syncwarp();
     // the groups that are not kept: n_groups - keep rounds of taking the smallest out (ties: the higher index goes)
@@ -984,7 +1003,7 @@ __global__ void __launch_bounds__(32 * MIX_ROUTE_WARPS) moe_route_kernel(const f
     }
     if (bi < 0) bi = 0;                           // fewer experts allowed than asked for: cannot happen with a checked configuration
     if (k == 0) first = s[bi];                    // the largest picked logit: the softmax's reference (mode 1)
-    float sv = mode ? expf(s[bi] - first) : s[bi];
+    float sv = mode == 1 ? expf(s[bi] - first) : s[bi];
     sum += sv;
     if (lane == 0) {
       idx[(size_t)t * top + k] = bi;
@@ -993,12 +1012,14 @@ __global__ void __launch_bounds__(32 * MIX_ROUTE_WARPS) moe_route_kernel(const f
     }
     __syncwarp();
   }
-  float f = mode ? 1.0f / sum : scale / (sum + 1e-20f);
+  float f = mode == 2 ? scale : mode ? 1.0f / sum : scale / (sum + 1e-20f);
   for (int k = lane; k < top; k += 32) wgt[(size_t)t * top + k] *= f;
 }
 
 // The clamped gate of an expert: g' * sigmoid(alpha * g') * (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
+// limit <= 0 stands for the gate without a clamp: silu(g) * u.
 __device__ __forceinline__ float glu_clamp_f(float g, float u, float limit, float alpha) {
+  if (!(limit > 0.f)) return g * sigmoid_f(g) * u;       // no limit: the plain gate silu(g) * u
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
   return g * sigmoid_f(alpha * g) * (u + 1.0f);

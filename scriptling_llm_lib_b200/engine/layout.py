@@ -3,7 +3,9 @@
 The reference runs blocks 0..L-1 once each over one cache per block (model_f32.go:371-373). Here
 the order is a list of schedule entries; an entry names the layer to run and the cache unit it
 uses, so a layer can appear twice (with a unit for each appearance) or read the unit that another
-entry wrote (`writes_cache=False`).
+entry wrote (`writes_cache=False`). An entry may also name stream inputs that run right before its layer (`before`,
+indices into the layout's `stream_parts`): parts that add to the residual stream between two layers, such as the vector
+that opens a pass over a run of layers that is gone through several times with the same weights.
 """
 from __future__ import annotations
 
@@ -18,6 +20,7 @@ class ScheduleEntry:
     layer: int
     cache_unit: int
     writes_cache: bool = True
+    before: tuple[int, ...] = ()        # stream inputs (ModelLayout.stream_parts) that run right before the layer
 
 
 @dataclass(frozen=True)
@@ -32,12 +35,16 @@ class ModelLayout:
     head: PartSpec                      # HEADS
     stop_ids: tuple[int, ...] = ()
     ignorable_tensors: tuple[str, ...] = field(default=())   # may be in the file without being used
+    stream_parts: tuple[PartSpec, ...] = ()                  # STREAM_INPUTS that schedule entries run before their layers
 
     def check(self) -> None:
         written: set[int] = set()
         for e in self.schedule:
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {e.layer}; the model has {len(self.layers)}")
+            for i in e.before:
+                if not 0 <= i < len(self.stream_parts):
+                    raise ValueError(f"schedule names stream input {i}; the model has {len(self.stream_parts)}")
             if e.writes_cache:
                 if e.cache_unit in written:
                     raise ValueError(f"cache unit {e.cache_unit} is written by two schedule entries")
@@ -48,3 +55,16 @@ class ModelLayout:
 
 def sequential_schedule(n_layers: int) -> tuple[ScheduleEntry, ...]:
     return tuple(ScheduleEntry(i, i, True) for i in range(n_layers))
+
+
+def looped_schedule(n_layers: int, start: int, stop: int, times: int, before_pass=None) -> tuple[ScheduleEntry, ...]:
+    """Layers 0 .. start - 1 once, layers start .. stop - 1 `times` times in a row with the same weights, then the rest once.
+    Every appearance of a layer has a cache unit of its own, numbered in running order. `before_pass(t)` -> the stream
+    inputs (indices) that run right before pass t's first layer."""
+    if not 0 <= start <= stop <= n_layers or times < 1:
+        raise ValueError(f"a loop over layers {start}..{stop - 1} of {n_layers}, {times} times")
+    order = [(i, ()) for i in range(start)]
+    for t in range(times):
+        order += [(i, tuple(before_pass(t)) if before_pass is not None and i == start else ()) for i in range(start, stop)]
+    order += [(i, ()) for i in range(stop, n_layers)]
+    return tuple(ScheduleEntry(layer, unit, True, before) for unit, (layer, before) in enumerate(order))

@@ -6,7 +6,7 @@ what a layer needs of the cache or whether its decode step can be captured is as
 from __future__ import annotations
 
 from ..cache.needs import CacheNeed, StateNeed
-from ..parts.base import EMBEDDINGS, HEADS, NORMS
+from ..parts.base import EMBEDDINGS, HEADS, NORMS, STREAM_INPUTS
 from ..parts.block import build_block
 from ..weights.spec import TensorSpec
 from .layout import ModelLayout
@@ -18,6 +18,7 @@ class DecoderModel:
         self.layout = layout
         self.embedding = EMBEDDINGS.build(layout.embedding)
         self.blocks = [build_block(spec) for spec in layout.layers]
+        self.stream_parts = [STREAM_INPUTS.build(spec) for spec in layout.stream_parts]
         self.final_norm = NORMS.build(layout.final_norm)
         self.head = HEADS.build(layout.head)
 
@@ -25,6 +26,7 @@ class DecoderModel:
         out = [self.embedding]
         for b in self.blocks:
             out.extend(b.parts())
+        out.extend(self.stream_parts)
         out.extend([self.final_norm, self.head])
         return out
 
@@ -49,18 +51,25 @@ class DecoderModel:
     def graph_safe(self) -> bool:
         """True when every block says its decode step launches the same work whatever the values
         (no host reads, no shapes that depend on data), so the step can be captured and replayed."""
-        return all(b.graph_safe() for b in self.blocks)
+        return all(b.graph_safe() for b in self.blocks) and all(getattr(p, "graph_safe", False) for p in self.stream_parts)
 
     def cache_needs(self) -> dict[int, CacheNeed | None]:
         """Need of every cache unit, asked of the block of the entry that writes it."""
         return {e.cache_unit: self.blocks[e.layer].cache_need() for e in self.layout.schedule if e.writes_cache}
 
-    def state_needs(self) -> dict[int, StateNeed | None]:
-        return {e.cache_unit: self.blocks[e.layer].state_need() for e in self.layout.schedule if e.writes_cache}
+    def state_needs(self) -> dict:
+        """Per-sequence state of fixed size: of every cache unit (asked of the block that writes it), and of the
+        embedding under the key "embedding" where it keeps some (the token before a step's first)."""
+        needs = {e.cache_unit: self.blocks[e.layer].state_need() for e in self.layout.schedule if e.writes_cache}
+        own = getattr(self.embedding, "state_need", None)
+        if own is not None and own() is not None:
+            needs["embedding"] = own()
+        return needs
 
     def elements_read_per_step(self) -> int:
         """Weight elements one decode step reads whatever the batch: every scheduled layer's parts
         (a layer that runs twice is read twice), the final norm and the head."""
         n = sum(p.elements_read_per_step() for e in self.layout.schedule for p in self.blocks[e.layer].parts())
+        n += sum(self.stream_parts[i].elements_read_per_step() for e in self.layout.schedule for i in e.before)
         return n + self.embedding.elements_read_per_step() + self.final_norm.elements_read_per_step() + \
             self.head.elements_read_per_step()

@@ -379,7 +379,9 @@ class Engine:
         schedule, blocks, rows = self.layout.schedule, self.model.blocks, residual.shape[0]
         for i, e in enumerate(schedule):
             block = blocks[e.layer]
-            nxt = blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            for j in e.before:                          # stream inputs that stand between two layers
+                delta = self.model.stream_parts[j].forward(residual, delta, ctx)
+            nxt = blocks[schedule[i + 1].layer] if i + 1 < len(schedule) and not schedule[i + 1].before else None
             if getattr(block, "folds_entry", False) and nxt is not None and getattr(nxt, "folds_entry", False):
                 # the layer behind this one says what its first norm would let this layer's last sublayer prepare
                 delta = block.forward(residual, delta, ctx, e.cache_unit, e.writes_cache,

@@ -1,4 +1,4 @@
-from . import (attention, block, delta_rule, embedding, experts, feedforward, latent_attention, linear_attention, norm, parallel, rglru,
+from . import (attention, block, delta_rule, embedding, experts, feedforward, latent_attention, linear_attention, norm, parallel, pass_vector, rglru,
                rotary, selective_scan, token_side)  # noqa: F401  (registers the built-in parts)
 from .base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, STREAM_INPUTS, Embedding, FeedForward,
                    Head, Mixer, Norm, Part, PartSpec, PositionEncoding, StreamInput)

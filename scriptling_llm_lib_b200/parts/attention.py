@@ -25,6 +25,16 @@ kernel that norms, rotates and fills the cache in float32: `conv_qk_norm_store` 
 keeps its float32 output on the chip (rows up to 51200 columns); `qk_norm_store` reads the float32 output of a
 convolution that ran by itself, or the projection. The attention kernels are the same ones.
 
+Four more, again none in the reference. `values_are_keys`: there is no value projection; a position's values are its keys
+as projected, before the rotation (the cache keeps both: the turned keys and the unturned ones as values; the key
+matrix is stacked twice into the one product, so every kernel behind it sees the usual q|k|v row). `softcap`: a score
+s = (q . k) * scale becomes softcap * tanh(s / softcap) before the softmax. `sink_name`: a stored number per head
+whose exponential joins the softmax's denominator; it has no key and no value, is neither scaled nor capped, and
+counts once whatever the number of keys. `gate_per="element"`: the gate matrix is [n_heads * v_dim, hidden] and the
+concatenated heads are multiplied element by element with the sigmoid of its product with the mixer's input
+("head", the default: one logit per head). Capped scores and sinks run on the attention kernels of the generic
+set in both precisions (scores, cap, softmax and sink float32).
+
 The position encoding is optional (`position=None`: queries and keys as projected). Storing keys
 and values in the cache is this mixer's own step, whatever the encoding: for an encoding that is a
 rotation by a table the store and the rotation are one kernel (or part of the q|k|v product's
@@ -56,7 +66,9 @@ class Attention(Mixer):
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PartSpec | None,
                  q_name: str, k_name: str, v_name: str, o_name: str, window: int | None = None,
                  scale: float | None = None, v_dim: int | None = None, value_norm_eps: float | None = None,
-                 chunk: int | None = None, conv: dict | None = None, qk_norm: dict | None = None, gate_name: str | None = None):
+                 chunk: int | None = None, conv: dict | None = None, qk_norm: dict | None = None, gate_name: str | None = None,
+                 values_are_keys: bool = False, softcap: float | None = None, sink_name: str | None = None,
+                 gate_per: str = "head"):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} key/value heads")
         if not 1 <= head_dim <= 512:
@@ -65,6 +77,23 @@ class Attention(Mixer):
             raise ValueError("an attention layer has a sliding window or chunks, not both")
         if chunk is not None and chunk < 1:
             raise ValueError(f"chunks of {chunk} positions")
+        if gate_per not in ("head", "element"):
+            raise ValueError(f"a gate per {gate_per!r}; known: head, element")
+        self.values_are_keys = bool(values_are_keys)
+        if self.values_are_keys:
+            if v_dim is not None and int(v_dim) != head_dim:
+                raise ValueError(f"values that are the keys are as wide as the keys ({head_dim}), not {v_dim}")
+            if conv is not None or value_norm_eps is not None:
+                raise ValueError("values that are the keys take neither a convolution nor a value norm")
+            v_name = k_name
+        self.softcap = float(softcap) if softcap else None
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"a cap on the scores must be positive, got {softcap}")
+        self.sink_name, self.sink = sink_name, None
+        self.plain_softmax = self.softcap is None and sink_name is None
+        if not self.plain_softmax and v_dim is not None and int(v_dim) != head_dim:
+            raise ValueError("capped scores and sinks run on kernels whose values are as wide as the keys")
+        self.gate_per = gate_per
         self.hidden, self.n_heads, self.n_kv_heads, self.head_dim, self.window = hidden, n_heads, n_kv_heads, head_dim, window
         self.chunk = int(chunk) if chunk else None
         # what the kernels take as `window`: > 0 a sliding window, < 0 chunks of that many positions, 0 every earlier key
@@ -80,7 +109,7 @@ class Attention(Mixer):
         self.gate_name = gate_name
         names, widths = [q_name, k_name, v_name], [qw, kw, vw]
         if gate_name is not None:               # the gates' logits ride in the same product, behind the values
-            names, widths = names + [gate_name], widths + [n_heads]
+            names, widths = names + [gate_name], widths + [n_heads if gate_per == "head" else n_heads * self.v_dim]
         self.qkv = Linear(names, widths, hidden)
         self.out = Linear([o_name], [hidden], n_heads * self.v_dim)
         self.q_only: Linear | None = None
@@ -96,7 +125,13 @@ class Attention(Mixer):
         return self.conv is not None or self.qk_norm is not None
 
     def tensor_specs(self):
-        specs = self.qkv.tensor_specs() + self.out.tensor_specs()
+        specs, seen = [], set()
+        for ts in self.qkv.tensor_specs() + self.out.tensor_specs():      # the key matrix may stand twice in the stacked product
+            if ts.name not in seen:
+                seen.add(ts.name)
+                specs.append(ts)
+        if self.sink_name is not None:
+            specs.append(TensorSpec(self.sink_name, (self.n_heads,), init="bias"))
         if self.conv is not None:
             specs += self.conv.tensor_specs()
         if self.qk_norm is not None:
@@ -108,6 +143,8 @@ class Attention(Mixer):
         self.qkv.bind(tensors, dtype, device)
         self.out.bind(tensors, dtype, device)
         self.q_only = self.qkv.rows(0, self.n_heads * self.head_dim)
+        if self.sink_name is not None:
+            self.sink = tensors[self.sink_name].float().contiguous()
         if self.conv is not None:
             self.conv.bind(tensors, dtype, device)
         if self.qk_norm is not None:
@@ -156,7 +193,7 @@ class Attention(Mixer):
     def takes_folded(self, ctx, rows: int) -> bool:
         """The q|k|v product can scale its own output rows: in a decode step of few rows, and in a long
         prompt step (the tensor-core product, with or without the rotation in its epilogue)."""
-        if self.prepared or self.gate_name is not None:
+        if self.prepared or self.gate_name is not None or not self.plain_softmax:
             return False
         path = self.qkv.fold_path(ctx, rows, ctx.dtype)
         return path is not None and self.q_only.fold_path(ctx, rows, ctx.dtype) == path and (ctx.is_decode or path == "tiles")
@@ -169,7 +206,20 @@ class Attention(Mixer):
     def _attend(self, qkv, x, ctx, kpages, vpages, block_table, fast_decode, fusion, writes):
         """The step's queries (the leading columns of `qkv`) over the cache -> [T, n_heads * v_dim]."""
         attn = torch.empty((x.shape[0], self.n_heads * self.v_dim), dtype=x.dtype, device=x.device)
-        if self.other_widths:
+        if not self.plain_softmax:
+            k = ctx.kernels
+            if not qkv.is_contiguous():
+                qkv = qkv.contiguous()
+            if ctx.is_decode and k.attn_decode_split_takes(self.head_dim, qkv.stride(0)):
+                n_split = k.attn_decode_splits(ctx.n_seqs, self.n_heads, self.n_kv_heads, ctx.max_pages, ctx.engine.sm_count)
+                part = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
+                                   device=x.device) if n_split > 1 else None
+                k.attn_decode_split(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, part, ctx.n_seqs, self.n_heads,
+                                    self.n_kv_heads, self.head_dim, self.span, self.scale, n_split, self.softcap, self.sink)
+            else:
+                k.attn_paged(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages, ctx.n_seqs, ctx.max_new,
+                             self.n_heads, self.n_kv_heads, self.head_dim, self.span, self.scale, self.softcap, self.sink)
+        elif self.other_widths:
             ctx.kernels.seq.attn_wide_value(qkv, attn, ctx.tok_pos, ctx.tok_seq, block_table, kpages, vpages, self.n_heads,
                                             self.n_kv_heads, self.head_dim, self.v_dim, self.span, self.scale)
         elif fast_decode:
@@ -232,8 +282,10 @@ class Attention(Mixer):
         fast_decode = (ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in DecodeKernels.HEAD_DIMS
                        and not self.other_widths)
         attn = self._attend(q, x, ctx, kpages, vpages, block_table, fast_decode, None, writes)
-        if self.gate_name is not None:
+        if self.gate_name is not None and self.gate_per == "head":
             ctx.kernels.gate.head_gate(attn, y[:, qw + kw + vw:], self.n_heads, self.v_dim)
+        elif self.gate_name is not None:            # a logit per element: "heads" of one column each
+            ctx.kernels.gate.head_gate(attn, y[:, qw + kw + vw:], self.n_heads * self.v_dim, 1)
         if fold is not None:
             return self.out.forward_folded(attn, ctx, fold=fold)
         return self.out.forward(attn, ctx, partials_ok=True)
@@ -244,7 +296,7 @@ class Attention(Mixer):
         else:
             folded = None
         kpages, vpages, block_table = ctx.unit_kv(unit)
-        if self.prepared or self.gate_name is not None:
+        if self.prepared or self.gate_name is not None or not self.plain_softmax:
             return self._forward_prepared(x, ctx, writes, state, kpages, vpages, block_table, fold)
         fast_decode = ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in DecodeKernels.HEAD_DIMS
         rotation = self.position.rotation() if self.position is not None else None

@@ -282,7 +282,43 @@ class PreNormInputBlock(Block):
         return self.stream_input.forward(residual, a, ctx)
 
 
+class ParallelInputBlock(Block):
+    """x += mixer(h) + feed_forward(h) with h = norm(x): ONE norm, and both sublayers read its output; then, where the layer
+    has one, a stream input (a part that reads the stream as it then stands and the step's tokens and adds to it). Roles:
+    `mixer_norm`, `mixer`, optionally `feed_forward`, optionally `stream_input`. The sublayers' outputs travel as a list of
+    addends (a feed-forward may itself answer with a list: routed experts beside an expert that every token uses), taken
+    into the stream in one pass by the stream input or by the norm that reads the stream next, so the norms named here must
+    take lists (`dynamic_tanh`). The mixer may keep per-sequence state (handed to it as `state=`)."""
+
+    def __init__(self, spec: LayerSpec):
+        self.mixer_norm = NORMS.build(_role(spec, "mixer_norm"))
+        self.mixer = MIXERS.build(_role(spec, "mixer"))
+        self.feed_forward = FEED_FORWARDS.build(spec.parts["feed_forward"]) if "feed_forward" in spec.parts else None
+        self.stream_input = STREAM_INPUTS.build(spec.parts["stream_input"]) if "stream_input" in spec.parts else None
+
+    def parts(self):
+        out = [self.mixer_norm, self.mixer]
+        if self.feed_forward is not None:
+            out.append(self.feed_forward)
+        if self.stream_input is not None:
+            out.append(self.stream_input)
+        return out
+
+    def forward(self, residual, delta, ctx, unit, writes):
+        st = ctx.unit_state(unit) if self.state_need() is not None else None
+        h = self.mixer_norm.forward(residual, delta, ctx)
+        a = self.mixer.forward(h, ctx, unit, writes, state=st) if st is not None else self.mixer.forward(h, ctx, unit, writes)
+        pending = list(a) if isinstance(a, (list, tuple)) else [a]
+        if self.feed_forward is not None:
+            f = self.feed_forward.forward(h, ctx)
+            pending += list(f) if isinstance(f, (list, tuple)) else [f]
+        if self.stream_input is None:
+            return pending
+        return self.stream_input.forward(residual, pending, ctx)
+
+
 ARRANGEMENTS.register("pre_norm", PreNormBlock)
+ARRANGEMENTS.register("parallel_input", ParallelInputBlock)
 ARRANGEMENTS.register("pre_norm_input", PreNormInputBlock)
 ARRANGEMENTS.register("sandwich_norm", SandwichNormBlock)
 ARRANGEMENTS.register("scaled_pre_norm", ScaledPreNormBlock)

@@ -21,6 +21,13 @@ given. Gate and up rows are stacked per expert ([experts, 2 ff, hidden]) and mul
 with widths the tensor cores take they are stacked in tiles of 16 (8 gate rows, their 8 up rows), so that a long
 step's grouped product applies the gate in its epilogue and writes the inner vector only.
 
+Three more. `router="grouped_softmax"`: the scores are the softmax of z over ALL experts; a run of experts is rated by its
+best score alone, the `keep_groups` best runs stay open, the `top` open experts with the highest scores are picked, and
+they count with their scores as they are, not renormalised (times `scale`); no stored correction. `act="silu_glu"`: an
+expert's inner vector is silu(Wg x) * (Wu x), the gate without a clamp (stacked and tiled like the clamped one).
+`shared`: a feed-forward (a `PartSpec` of the FEED_FORWARDS registry) that every token runs beside its chosen experts; the
+part then answers with a list of two addends, the routed sum and the shared expert's output.
+
 The experts' matrices are stacked [experts, ff, hidden] and [experts, hidden, ff]. A step of few
 rows runs every (token, chosen expert) pair by itself (each streams its expert's matrices once); a
 longer step groups the pairs by expert on the device and runs tiles of rows per expert: in bfloat16
@@ -39,7 +46,7 @@ from .base import FEED_FORWARDS, FeedForward
 from .linear import Linear
 
 ACTS = ("gelu_tanh", "relu_squared", "silu")
-ROUTERS = ("grouped_sigmoid", "top_softmax")
+ROUTERS = ("grouped_sigmoid", "top_softmax", "grouped_softmax")
 
 
 class ActFeedForward(FeedForward):
@@ -80,9 +87,9 @@ class RoutedExperts(FeedForward):
     def __init__(self, hidden: int, intermediate: int, experts: int, top: int, n_groups: int, keep_groups: int, scale: float,
                  router_name: str, correction_name: str | None, up_names: list, down_names: list, act: str = "relu_squared",
                  router: str = "grouped_sigmoid", gate_names: list | None = None, limit: float | None = None,
-                 alpha: float = 1.702):
-        if act not in ("relu_squared", "clamped_glu"):
-            raise ValueError("the experts' kernels apply the square of relu or the clamped gate (clamped_glu)")
+                 alpha: float = 1.702, shared=None):
+        if act not in ("relu_squared", "clamped_glu", "silu_glu"):
+            raise ValueError("the experts' kernels apply the square of relu, the clamped gate (clamped_glu) or the plain gate (silu_glu)")
         if router not in ROUTERS:
             raise ValueError(f"router {router!r}; known: {', '.join(ROUTERS)}")
         if len(up_names) != experts or len(down_names) != experts:
@@ -92,12 +99,18 @@ class RoutedExperts(FeedForward):
             if gate_names is None or len(gate_names) != experts or limit is None or not float(limit) > 0:
                 raise ValueError("gated experts need a gate matrix each and a positive limit")
             self.glu = (float(limit), float(alpha))
+        elif act == "silu_glu":
+            if gate_names is None or len(gate_names) != experts:
+                raise ValueError("gated experts need a gate matrix each")
+            self.glu = (0.0, 1.0)           # a limit of 0: the kernels' word for the gate without a clamp
         self.gate_names = list(gate_names) if self.glu is not None else None
+        self.router_kind = router
         self.top_softmax = router == "top_softmax"
         if self.top_softmax and n_groups != 1:
             raise ValueError("the top_softmax router knows no runs of experts")
-        if not self.top_softmax and correction_name is None:
+        if router == "grouped_sigmoid" and correction_name is None:
             raise ValueError("the grouped_sigmoid router needs its correction")
+        self.shared = FEED_FORWARDS.build(shared) if shared is not None else None
         if n_groups < 1 or experts % n_groups or not 1 <= keep_groups <= n_groups:
             raise ValueError(f"{experts} experts cannot form {n_groups} equal groups of which {keep_groups} are kept")
         if not 1 <= top <= keep_groups * (experts // n_groups):
@@ -116,14 +129,19 @@ class RoutedExperts(FeedForward):
             if self.glu is not None:
                 specs.append(TensorSpec(self.gate_names[j], (self.F, self.hidden)))
             specs += [TensorSpec(u, (self.F, self.hidden)), TensorSpec(d, (self.hidden, self.F))]
+        if self.shared is not None:
+            specs += self.shared.tensor_specs()
         return specs
 
     def elements_read_per_step(self) -> int:
         """A decode step reads the router and, per token, `top` experts: counted once (one token)."""
-        return self.E * self.hidden + self.E + self.top * (3 if self.glu is not None else 2) * self.F * self.hidden
+        own = self.shared.elements_read_per_step() if self.shared is not None else 0
+        return own + self.E * self.hidden + self.E + self.top * (3 if self.glu is not None else 2) * self.F * self.hidden
 
     def bind(self, tensors, dtype, device):
         self.router.bind(tensors, dtype, device)
+        if self.shared is not None:
+            self.shared.bind(tensors, dtype, device)
         self.correction = tensors[self.correction_name].float().contiguous() if self.correction_name is not None else None
         self.tiled = False
         if self.glu is not None:                                                         # [E, 2 F, hidden]: gate rows, up rows
@@ -147,13 +165,19 @@ class RoutedExperts(FeedForward):
         return x.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.F % 8 == 0 and x.data_ptr() % 16 == 0
 
     def forward(self, x, ctx):
+        routed = self._routed(x, ctx)
+        if self.shared is None:
+            return routed
+        return [routed, self.shared.forward(x, ctx)]
+
+    def _routed(self, x, ctx):
         k = ctx.kernels.mix
         T, dev = x.shape[0], x.device
         pairs = T * self.top
         idx = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         wgt = torch.empty((T, self.top), dtype=torch.float32, device=dev)
         z = self.router.forward(x, ctx, out_dtype=torch.float32)                  # logits, float32 sums
-        k.moe_route(z, self.correction, idx, wgt, self.n_groups, self.keep, self.top, self.scale, top_softmax=self.top_softmax)
+        k.moe_route(z, self.correction, idx, wgt, self.n_groups, self.keep, self.top, self.scale, router=self.router_kind)
         if pairs <= self.PAIRS_ONE_BY_ONE:
             hid = torch.empty((pairs, self.F), dtype=x.dtype, device=dev)
             out = torch.empty((self.top, T, self.hidden), dtype=torch.float32, device=dev)

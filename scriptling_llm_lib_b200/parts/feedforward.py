@@ -65,4 +65,49 @@ class SwiGLU(FeedForward):
         return h
 
 
+class ClampedGLU(FeedForward):
+    """Dense feed-forward with the clamped gate (absent in the reference): g = min(Wg x, limit), u = clamp(Wu x, -limit, limit),
+    y = Wd (g * sigmoid(alpha g) * (u + 1)). Gate and up rows are stacked into one product; in bfloat16 with widths in
+    multiples of 8 they are kept in tiles of 16 (8 gate rows, their 8 up rows), and a long step runs the grouped tensor-core
+    product with one group, whose epilogue applies the gate on the float sums and writes the inner vector only. Otherwise
+    the product's sums pass the gate in a kernel of its own."""
+    graph_safe = True
+
+    def __init__(self, hidden: int, intermediate: int, gate_name: str, up_name: str, down_name: str, limit: float,
+                 alpha: float = 1.702):
+        if not float(limit) > 0:
+            raise ValueError(f"the clamped gate needs a positive limit, got {limit}")
+        self.hidden, self.intermediate, self.glu = hidden, intermediate, (float(limit), float(alpha))
+        self.gate_up = Linear([gate_name, up_name], [intermediate, intermediate], hidden)
+        self.down = Linear([down_name], [hidden], intermediate)
+
+    def tensor_specs(self):
+        return self.gate_up.tensor_specs() + self.down.tensor_specs()
+
+    def bind(self, tensors, dtype, device):
+        self.gate_up.bind(tensors, dtype, device)
+        self.down.bind(tensors, dtype, device)
+        F = self.intermediate
+        self.tiled = dtype == torch.bfloat16 and F % 8 == 0 and self.hidden % 8 == 0
+        if self.tiled:
+            w = self.gate_up.weight
+            self.gate_up.weight = w.view(2, F // 8, 8, self.hidden).permute(1, 0, 2, 3).reshape(2 * F, self.hidden).contiguous()
+        self.one_group = torch.zeros((128,), dtype=torch.int32, device=device)      # the one group every row tile belongs to
+
+    def forward(self, x, ctx):
+        T, F = x.shape[0], self.intermediate
+        h = torch.empty((T, F), dtype=x.dtype, device=x.device)
+        tc = ctx.kernels.tensor_core if x.dtype == torch.bfloat16 else None
+        if self.tiled and tc is not None and T > tc.SKINNY_MAX_M and x.data_ptr() % 16 == 0 and x.is_contiguous():
+            tiles = -(-T // 128)
+            if self.one_group.shape[0] < tiles:
+                self.one_group = torch.zeros((tiles,), dtype=torch.int32, device=x.device)
+            tc.gemm_grouped(x, self.gate_up.weight.unsqueeze(0), h, self.one_group[:tiles], ctx.err_flag, glu=self.glu)
+        else:
+            gu = self.gate_up.forward(x, ctx)
+            ctx.kernels.mix.glu_clamp(gu, h, self.glu[0], self.glu[1], tiled=self.tiled)
+        return self.down.forward(h, ctx, partials_ok=True)
+
+
 FEED_FORWARDS.register("swiglu", SwiGLU)
+FEED_FORWARDS.register("clamped_glu", ClampedGLU)

@@ -20,6 +20,11 @@ products per query and key than asking the latent, which is wider than a head.
 A layer built with `shares_cache=True` has no Wdkv: it runs with `writes=False` on the unit another
 latent-attention layer of the same widths and rotation wrote, with its own Wq, Wuk, Wuv and Wo.
 
+Three options. `q_rank`: the queries go through a latent of their own, c_q = (Wdq h) / rms * w and q = Wuq c_q (the
+down-projection leaves float32 sums, the norm is float32, and `q_name` is not used). `pairing="half"`: the rotated part
+turns dim i with dim i + rot / 2 instead of neighbours. `gate_name`: a matrix [n_heads, hidden] on the mixer's input; head
+i's output is multiplied by the sigmoid of its logit before Wo (the logits ride in the down-projection's product).
+
 The products run in the engine's dtype and the cache holds it; the latent's norm, the rotation,
 the absorbed queries, scores, softmax and sums over the latent are float32.
 """
@@ -38,8 +43,10 @@ class LatentAttention(Mixer):
     MAX_RANK = 1024          # the kernel keeps a lane's share of the latent sum in registers
 
     def __init__(self, hidden: int, n_heads: int, dim: int, rot_dim: int, v_dim: int, kv_rank: int, scale: float,
-                 position: PartSpec | None, norm_eps: float, q_name: str, uk_name: str, uv_name: str, o_name: str,
-                 dkv_name: str | None = None, dkv_norm_name: str | None = None, shares_cache: bool = False):
+                 position: PartSpec | None, norm_eps: float, q_name: str | None, uk_name: str, uv_name: str, o_name: str,
+                 dkv_name: str | None = None, dkv_norm_name: str | None = None, shares_cache: bool = False,
+                 q_rank: int | None = None, dq_name: str | None = None, dq_norm_name: str | None = None, uq_name: str | None = None,
+                 gate_name: str | None = None):
         if kv_rank < 1 or kv_rank > self.MAX_RANK:
             raise ValueError(f"latent of width {kv_rank}: the attention kernel takes 1..{self.MAX_RANK}")
         if not shares_cache and (dkv_name is None or dkv_norm_name is None):
@@ -49,24 +56,47 @@ class LatentAttention(Mixer):
         self.position = POSITION_ENCODINGS.build(position) if position is not None else None
         qw = n_heads * (dim + rot_dim)
         self.q_width = qw
-        if shares_cache:
-            self.proj = Linear([q_name], [qw], hidden)
+        self.q_rank = int(q_rank) if q_rank else None
+        self.gate_name, self.dq_norm_name = gate_name, dq_norm_name
+        if self.q_rank is not None:
+            if dq_name is None or dq_norm_name is None or uq_name is None:
+                raise ValueError("queries through a latent need its down-projection, norm weight and up-projection")
+            self.q_down = Linear([dq_name], [self.q_rank], hidden)
+            self.q_up = Linear([uq_name], [qw], self.q_rank)
+            names, widths = [], []
         else:
-            self.proj = Linear([q_name, dkv_name], [qw, kv_rank + rot_dim], hidden)
+            if q_name is None:
+                raise ValueError("a latent-attention layer needs a query projection, direct or through a latent")
+            self.q_down = self.q_up = None
+            names, widths = [q_name], [qw]
+        self.q_cols = widths[0] if widths else 0           # columns of the stacked product that are queries
+        if not shares_cache:
+            names, widths = names + [dkv_name], widths + [kv_rank + rot_dim]
+        if gate_name is not None:
+            names, widths = names + [gate_name], widths + [n_heads]
+        self.proj = Linear(names, widths, hidden) if names else None
         self.out = Linear([o_name], [hidden], n_heads * v_dim)
         self.kv_up = Linear([uk_name, uv_name], [n_heads * dim, n_heads * v_dim], kv_rank)
         self.hd = (max(dim + rot_dim, v_dim) + 3) // 4 * 4      # one width for keys, values and queries of the per-head form
         self.uk_name, self.uv_name, self.dkv_norm_name = uk_name, uv_name, dkv_norm_name
 
     def tensor_specs(self):
-        specs = self.proj.tensor_specs() + self.out.tensor_specs() + [
+        specs = (self.proj.tensor_specs() if self.proj is not None else []) + self.out.tensor_specs()
+        if self.q_rank is not None:
+            specs += self.q_down.tensor_specs() + self.q_up.tensor_specs() + [TensorSpec(self.dq_norm_name, (self.q_rank,), init="norm_weight")]
+        specs += [
             TensorSpec(self.uk_name, (self.H * self.D, self.R)), TensorSpec(self.uv_name, (self.H * self.V, self.R))]
         if not self.shares_cache:
             specs.append(TensorSpec(self.dkv_norm_name, (self.R,), init="norm_weight"))
         return specs
 
     def bind(self, tensors, dtype, device):
-        self.proj.bind(tensors, dtype, device)
+        if self.proj is not None:
+            self.proj.bind(tensors, dtype, device)
+        if self.q_rank is not None:
+            self.q_down.bind(tensors, dtype, device)
+            self.q_up.bind(tensors, dtype, device)
+            self.q_norm_w = tensors[self.dq_norm_name].float().contiguous()
         self.out.bind(tensors, dtype, device)
         self.wuk, self.wuv = tensors[self.uk_name], tensors[self.uv_name]
         self.kv_up.bind(tensors, dtype, device)
@@ -115,7 +145,13 @@ class LatentAttention(Mixer):
             ctx.scratch["latent_heads_table"] = made
         return made
 
-    def _per_head(self, q, ctx, pages, block_table):
+    def _finish(self, attn, gate, width, out, ctx):
+        """The gate per head (where the layer has one) and the output product."""
+        if gate is not None:
+            ctx.kernels.gate.head_gate(attn, gate, self.H, width)
+        return out.forward(attn, ctx, partials_ok=True)
+
+    def _per_head(self, q, ctx, pages, block_table, gate=None):
         """The prompt from position 0: keys [Wuk c | rotated part] and values Wuv c per head for the step's rows, then
         the library's attention kernel for keys and values of one width over pages of their own. Costs
         (dim + rot_dim + v_dim) products per query, key and head instead of (2 kv_rank + rot_dim)."""
@@ -132,7 +168,7 @@ class LatentAttention(Mixer):
         attn = torch.empty((T, self.H * self.hd), dtype=q.dtype, device=dev)
         ctx.kernels.attn_paged(qt, attn, ctx.seq_start, ctx.seq_pos0, table, kt, vt, ctx.n_seqs, ctx.max_new, self.H, self.H,
                                self.hd, None, self.scale)
-        return self.out_wide.forward(attn, ctx, partials_ok=True)
+        return self._finish(attn, gate, self.hd, self.out_wide, ctx)
 
     def forward(self, x, ctx, unit, writes):
         if writes == self.shares_cache:
@@ -140,17 +176,28 @@ class LatentAttention(Mixer):
         k = ctx.kernels.mix
         pages, _, block_table = ctx.unit_kv(unit)
         T = x.shape[0]
-        proj = self.proj.forward(x, ctx)                                         # [T, q (| latent and key part, raw)]
-        q = proj[:, :self.q_width]
-        table, rot = None, 0
+        proj = self.proj.forward(x, ctx) if self.proj is not None else None     # [T, (q |) (latent and key part, raw |) (gate logits)]
+        if self.q_rank is not None:                                              # queries through their own normed latent
+            cq = self.q_down.forward(x, ctx, out_dtype=torch.float32)
+            cqn = torch.empty((T, self.q_rank), dtype=x.dtype, device=x.device)
+            ctx.kernels.add_rmsnorm(cq, None, None, self.q_norm_w, cqn, self.eps)
+            q = self.q_up.forward(cqn, ctx)
+        else:
+            q = proj[:, :self.q_width]
+        at = self.q_cols
+        dkv = None
+        if writes:
+            dkv = proj[:, at:at + self.R + self.P]
+            at += self.R + self.P
+        gate = proj[:, at:at + self.H] if self.gate_name is not None else None
+        table, rot, half = None, 0, False
         if self.position is not None:
             table, rot, interleaved = self.position.rotation()
-            if not interleaved:
-                raise ValueError("latent attention rotates adjacent pairs")
-        k.latent_store(q, self.H, self.D, proj[:, self.q_width:] if writes else None, self.norm_w, self.eps, table, rot, ctx,
-                       block_table, pages if writes else None, self.R, self.P)
+            half = not interleaved
+        k.latent_store(q, self.H, self.D, dkv, self.norm_w, self.eps, table, rot, ctx,
+                       block_table, pages if writes else None, self.R, self.P, half=half)
         if ctx.from_start and not ctx.is_decode and ctx.max_new >= self.PER_HEAD_MIN_ROWS:
-            return self._per_head(q, ctx, pages, block_table)
+            return self._per_head(q, ctx, pages, block_table, gate)
         qa = torch.empty((T, self.H, self.R + self.P), dtype=torch.float32, device=x.device)
         k.latent_absorb(q, self.wuk, qa, self.H, self.D, self.P, self.R, self.scale)
         n_split = self.splits(ctx)
@@ -159,7 +206,7 @@ class LatentAttention(Mixer):
         attn = torch.empty((T, self.H * self.V), dtype=x.dtype, device=x.device)
         olat = torch.empty((T, self.H, self.R), dtype=torch.float32, device=x.device)
         k.latent_expand(part, olat, self.wuv, attn, self.H, self.V, self.R, n_split)
-        return self.out.forward(attn, ctx, partials_ok=True)
+        return self._finish(attn, gate, self.V, self.out, ctx)
 
 
 MIXERS.register("latent_attention", LatentAttention)

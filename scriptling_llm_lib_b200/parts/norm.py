@@ -94,6 +94,31 @@ class WeightedNorm(Norm):
 
 
 @dataclass
+class WithRowVector:
+    """A pending addend (`inner`: None or any form a norm takes) together with a vector float32 [width] that every row of
+    the stream still has to take: x += inner; x += vector. The next reader of the stream adds both in its own pass."""
+    inner: Any
+    vector: Any
+
+
+def take_into_stream(residual, delta, ctx, xb=None) -> None:
+    """Adds a pending addend of any form into the stream by itself (no norm follows): None, a tensor in either form, a
+    list of such tensors, an `RmsNormedAddend`, and any of them inside a `WithRowVector`. `xb` (the engine's dtype,
+    [T, width]) receives the rounded stream."""
+    vec = None
+    if isinstance(delta, WithRowVector):
+        delta, vec = delta.inner, delta.vector
+    if isinstance(delta, RmsNormedAddend):
+        ctx.kernels.gate.add_rms_normed(residual, delta.y, delta.weight, delta.eps, vec=vec)
+        delta, vec = None, None
+    if isinstance(delta, NormedAddend):
+        raise ValueError("an addend that still has to pass a norm of its own is taken in by the norm that reads the stream next")
+    addends = [] if delta is None else list(delta) if isinstance(delta, (list, tuple)) else [delta]
+    if addends or vec is not None or xb is not None:
+        ctx.kernels.gate.add_list_cast(residual, addends, xb, vec)
+
+
+@dataclass
 class NormedAddend:
     """A sublayer's output that passes a norm of its own before it joins the residual stream:
     x += norm(y). `y` is [T, width] (the engine's dtype or float32) or float32 [P, T, width] partial
@@ -131,6 +156,22 @@ class DynamicTanh(Norm):
         return self.weight, self.bias, self.alpha
 
     def forward(self, residual, delta, ctx, rows=None):
+        """Besides a tensor and a `NormedAddend`, the pending addend may be an `RmsNormedAddend` (one kernel divides it by its
+        root mean square, adds it and norms the row), a list of tensors, and any of these inside a `WithRowVector`."""
+        vec = None
+        if isinstance(delta, WithRowVector):
+            delta, vec = delta.inner, delta.vector
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        if isinstance(delta, RmsNormedAddend):
+            y = torch.empty((n, self.width), dtype=ctx.dtype, device=residual.device)
+            ctx.kernels.gate.add_rms_normed(residual, delta.y, delta.weight, delta.eps, rows=rows, vec=vec,
+                                            dyt=(self.weight, self.bias, self.alpha, y))
+            return y
+        if isinstance(delta, (list, tuple)) or vec is not None:
+            if isinstance(delta, NormedAddend):
+                raise ValueError("a row vector does not travel with an addend that has a norm of its own")
+            take_into_stream(residual, WithRowVector(delta, vec) if vec is not None else delta, ctx)
+            delta = None
         addend, post = delta, None
         if isinstance(delta, NormedAddend):
             addend, post = delta.y, delta.norm.terms()

@@ -20,7 +20,7 @@ import torch
 from ..weights.spec import TensorSpec
 from .base import STREAM_INPUTS, StreamInput
 from .linear import Linear
-from .norm import RmsNormedAddend
+from .norm import RmsNormedAddend, take_into_stream
 
 
 class TokenSideInput(StreamInput):
@@ -56,7 +56,10 @@ class TokenSideInput(StreamInput):
         k = ctx.kernels.gate
         T = residual.shape[0]
         xb = torch.empty((T, self.width), dtype=ctx.dtype, device=residual.device)
-        k.add_cast(residual, delta, xb)                                  # the stream takes the sublayer's output; xb = its rounding
+        if delta is None or isinstance(delta, torch.Tensor):
+            k.add_cast(residual, delta, xb)                              # the stream takes the sublayer's output; xb = its rounding
+        else:                                                            # several addends, or one of the composite forms
+            take_into_stream(residual, delta, ctx, xb=xb)
         a = self.gate.forward(xb, ctx)
         g = torch.empty((T, self.dim), dtype=ctx.dtype, device=residual.device)
         k.gelu_mul_rows(a, ctx.token_ids, self.table, self.column, g)
