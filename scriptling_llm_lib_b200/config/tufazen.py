@@ -223,7 +223,7 @@ def _layer(e, where: str) -> TufazenLayerConfig:
     if kind == "attention":
         kv_heads = m.integer("kv_heads", minimum=1)
         if heads % kv_heads:
-            raise ConfigError(f"{mw}: {heads} heads cannot share {kv_heads} key/value heads")
+            raise ConfigError(f"{mw}: 'kv_heads' ({kv_heads}) must divide 'heads' ({heads})")
         if vdim != dim:
             raise ConfigError(f"{mw}: the values are the keys, so 'vdim' ({vdim}) must equal 'dim' ({dim})")
         mixer = TufazenAttentionConfig(heads, kv_heads, dim, vdim, m.number("scale"), m.number("softcap", default=None, positive=True),
