@@ -527,8 +527,37 @@ def belasun_config(z):
             "logit_softcap": 25.0, "norm": {"eps": 1e-6}, "token_side": {"dim": z["side"]}, "vocab": DESIGN_VOCAB, "width": z["width"]}
 
 
+# The Tufazen decoder (attention whose values are its keys with capped scores, sinks and an elementwise gate, with a dense
+# clamped-gate feed-forward; latent attention with queries through a latent and a gate per head, with routed experts in
+# groups beside a shared expert; one norm for both sublayers; a pair-table embedding; a per-layer input from the token)
+# at layer sizes that resemble real models of its kinds: heads of 128 of which 64 dims turn, a latent of 512 (256) with
+# 128 + 64 query/key dims a head and a query latent of 1536 (768), 64 (32) experts of which 6 (4) are used. Four layers of
+# which the first two are gone through twice: six layer runs, as many as the Llama decoder beside it has layers (same
+# width, heads and dense feed-forward).
+TUFAZEN_SIZES = {
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, vdim=128, rot_dim=64, rank=256, q_rank=768, ff=4096, experts=32, top=4,
+                  n_groups=4, keep=2, expert_ff=704, shared_ff=1408, side=128, groups=1),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, rot_dim=64, rank=512, q_rank=1536, ff=8192, experts=64, top=6,
+                  n_groups=8, keep=3, expert_ff=1408, shared_ff=2816, side=256, groups=1),
+}
+
+
+def tufazen_config(z):
+    att = {"type": "attention", "mlp": {"ff": z["ff"], "kind": "dense", "limit": 7.0}, "mixer": {
+        "dim": z["dim"], "heads": z["heads"], "kv_heads": z["kv_heads"], "scale": z["dim"] ** -0.5, "softcap": 30.0, "vdim": z["dim"],
+        "rot": {"base": 10000.0, "dims": z["dim"] // 2, "scaling": {"factor": 8.0, "fast": 32.0, "original": 4096, "slow": 1.0}}}}
+    lat = {"type": "latent_attention", "mixer": {
+        "dim": z["dim"], "heads": z["heads"], "kv_rank": z["rank"], "q_rank": z["q_rank"], "rot_dim": z["rot_dim"],
+        "rot": {"base": 10000.0, "dims": z["rot_dim"]}, "scale": (z["dim"] + z["rot_dim"]) ** -0.5, "vdim": z["vdim"]},
+        "mlp": {"expert": {"ff": z["expert_ff"]}, "kind": "moe", "shared": {"ff": z["shared_ff"]}, "router": {
+            "experts": z["experts"], "groups": {"count": z["n_groups"], "keep": z["keep"]}, "top": z["top"]}}}
+    return {"architecture": "Tufazen", "embedding": {"bigram": {"buckets": 100003, "mul_cur": 31, "mul_prev": 1009}},
+            "layers": [att, lat, att, lat], "logit_scale": 0.5, "loop": {"start": 0, "stop": 2, "times": 2}, "norm": {"eps": 1e-6},
+            "token_side": {"dim": z["side"]}, "vocab": DESIGN_VOCAB, "width": z["width"]}
+
+
 DESIGNS = {"sozilix": (DESIGN_SIZES, sozilix_config, 3), "muvorax": (MUVORAX_SIZES, muvorax_config, 6),
-           "belasun": (BELASUN_SIZES, belasun_config, 4)}
+           "belasun": (BELASUN_SIZES, belasun_config, 4), "tufazen": (TUFAZEN_SIZES, tufazen_config, 6)}
 
 
 def llama_like(z, max_positions, layers_per_group=3):
