@@ -53,6 +53,8 @@ struct FtArgs {
   int* err;
   int n_qt, n_seqs, n_items;   // query tiles per sequence (of the longest), sequences, work items
   int pair_heads;              // pair kernel: 1: an item is heads 2i, 2i+1 on one query tile; 0: query tiles 2i, 2i+1 of one head
+  float softcap;               // > 0: a score s (scaled) becomes softcap * tanh(s / softcap) before the softmax
+  const float* sink;           // [H] or null: exp(sink[h]) joins head h's denominator, with no key and no value
 };
 
 // What a block works on in its r-th round.
@@ -88,6 +90,17 @@ __device__ __forceinline__ float ft_ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// tanh(x) = 1 - 2 / (1 + 2^(2 x log2 e)): two special-function instructions, absolute error of a few 1e-7, exact limits
+__device__ __forceinline__ float ft_tanh(float x) {
+  float t = ft_ex2(x * (2.0f * FT_LOG2E)), r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + t));
+  return fmaf(-2.0f, r, 1.0f);
+}
+// A raw score s (the product's sum, before the scale) capped in place: the softmax below multiplies by the scale, so the
+// capped score is handed on as (cap / scale) * tanh(s * scale / cap).
+__device__ __forceinline__ uint32_t ft_cap(uint32_t s, float cap_out, float cap_in) {
+  return __float_as_uint(cap_out * ft_tanh(__uint_as_float(s) * cap_in));
 }
 __device__ __forceinline__ float ft_max3(float a, float b, float c) {
   float y;
@@ -270,6 +283,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tmem_ld32(t_lane + a * 64, s0);
       tmem_ld32(t_lane + a * 64 + 32, s1);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (p.softcap > 0.f) {
+        const float cap_out = p.softcap / p.scale, cap_in = p.scale / p.softcap;
+#pragma unroll
+        for (int i = 0; i < 32; i++) { s0[i] = ft_cap(s0[i], cap_out, cap_in); s1[i] = ft_cap(s1[i], cap_out, cap_in); }
+      }
       // ---- mask, row maximum (raw scores; four independent chains)
       bool need_mask = (t * FT_BK + FT_BK - 1 > qpos) || t * FT_BK < qfirst;
       if (need_mask) {
@@ -365,6 +383,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (ok) ok = mbar_wait(b_ofull + 8 * ((J0 + n_tiles - 1) & 1), ((J0 + n_tiles - 1) >> 1) & 1, abort);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (p.sink != nullptr) l = (m_ref == -INFINITY) ? 1.f : l + ft_ex2(p.sink[h] * FT_LOG2E - m_ref * sc);
       float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = p.out + (size_t)(row0 + r0 + r) * ((size_t)p.H * FT_HD) + (size_t)h * FT_HD;
 #pragma unroll 1
@@ -675,6 +694,11 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         __syncwarp();
         if (lane == 0) mbar_arrive(b_sempty + 8 * bf);
       }
+      if (p.softcap > 0.f) {
+        const float cap_out = p.softcap / p.scale, cap_in = p.scale / p.softcap;
+#pragma unroll
+        for (int i = 0; i < 64; i++) s[i] = ft_cap(s[i], cap_out, cap_in);
+      }
       ft_mask(s, t, qpos, qfirst);
       mx = ft_rowmax(s);
       // ---- move the reference maximum only when the row's maximum has outgrown it by 2^8
@@ -746,6 +770,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (ok) ok = mbar_wait(b_ofull + 8 * ((J0 + n_tiles - 1) & 1), ((J0 + n_tiles - 1) >> 1) & 1, abort);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (p.sink != nullptr) l = (m_ref == -INFINITY) ? 1.f : l + ft_ex2(p.sink[sb.h] * FT_LOG2E - m_ref * sc);
       float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = p.out + (size_t)(it.row0 + sb.r0 + r) * ((size_t)p.H * FT_HD) + (size_t)sb.h * FT_HD;
 #pragma unroll 1
@@ -821,7 +846,7 @@ static int fp_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
 SLLM_EXPORT int sllm_attn_prefill_tc_bf16(const void* q, int q_ld, int T, void* out, const int* seq_start, const int* seq_pos0,
                                           const int* block_table, int max_pages, const void* kpages, const void* vpages,
                                           long long n_pages, int B, int max_new, int H, int G, int hd, int window, float scale,
-                                          int* err, cudaStream_t stream) {
+                                          float softcap, const float* sink, int* err, cudaStream_t stream) {
   if (B <= 0 || max_new <= 0) return 0;
   if ((hd != 64 && hd != 128) || G < 1 || H % G != 0 || (q_ld & 7) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
       ((uintptr_t)kpages & 15) || ((uintptr_t)vpages & 15))
@@ -846,13 +871,13 @@ SLLM_EXPORT int sllm_attn_prefill_tc_bf16(const void* q, int q_ld, int T, void* 
     if (e != cudaSuccess) return (int)e;
   }
   if (hd == 64) {
-    FtArgs a{(bf16*)out, seq_start, seq_pos0, block_table, max_pages, H, G, window, scale, err, n_qt, B, (int)n_items, 0};
+    FtArgs a{(bf16*)out, seq_start, seq_pos0, block_table, max_pages, H, G, window, scale, err, n_qt, B, (int)n_items, 0, softcap, sink};
     dim3 grid((unsigned)(n_items < 2LL * sm_count ? n_items : 2LL * sm_count));     // two blocks per SM that stay
     return ft_launch<64, 3>(mq, mk, mv, a, grid, stream);
   }
   int pair_heads = ((H / G) % 2 == 0) ? 1 : 0;
   n_items = pair_heads ? (long long)(H / 2) * n_qt * B : (long long)H * ((n_qt + 1) / 2) * B;
-  FtArgs a{(bf16*)out, seq_start, seq_pos0, block_table, max_pages, H, G, window, scale, err, n_qt, B, (int)n_items, pair_heads};
+  FtArgs a{(bf16*)out, seq_start, seq_pos0, block_table, max_pages, H, G, window, scale, err, n_qt, B, (int)n_items, pair_heads, softcap, sink};
   dim3 grid((unsigned)(n_items < (long long)sm_count ? n_items : (long long)sm_count));       // one block per SM that stays
   return fp_launch<128, 4>(mq, mk, mv, a, grid, stream);
 }

@@ -454,14 +454,17 @@ class PrefillAttentionTC:
         self.lib.sllm_attn_prefill_tc_bf16.restype = c_int
 
     def attn(self, q, out, seq_start, seq_pos0, block_table, kpages, vpages, n_seqs, max_new, n_heads, n_kv, head_dim,
-             window, scale, err_flag):
+             window, scale, err_flag, softcap=None, sink=None):
+        """`softcap`: a score s becomes softcap * tanh(s / softcap) before the softmax; `sink` float32 [n_heads]: exp(sink[h])
+        joins head h's denominator with no key and no value."""
         _check(self.lib.sllm_attn_prefill_tc_bf16(
             _ptr(q, torch.bfloat16, "q"), c_int(q.shape[1]), c_int(q.shape[0]), _ptr(out, torch.bfloat16, "out"),
             _ptr(seq_start, torch.int32, "seq_start"), _ptr(seq_pos0, torch.int32, "seq_pos0"),
             _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]),
             _ptr(kpages, torch.bfloat16, "kpages"), _ptr(vpages, torch.bfloat16, "vpages"), c_longlong(kpages.shape[0]),
             c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(window or 0), c_float(scale),
-            _ptr(err_flag, torch.int32, "err_flag"), _stream()), "attn_prefill_tc")
+            c_float(softcap or 0.0), _ptr(sink, torch.float32, "sink"), _ptr(err_flag, torch.int32, "err_flag"), _stream()),
+            "attn_prefill_tc")
 
 
 class DecodeKernels:
@@ -472,7 +475,7 @@ class DecodeKernels:
     def __init__(self):
         self.lib = load_library("decode_bf16")
         for n in ("sllm_gemm_small_m_bf16", "sllm_gemm_small_m_fold_bf16", "sllm_attn_decode_bf16",
-                  "sllm_attn_decode_merged_bf16", "sllm_attn_decode_rope_bf16"):
+                  "sllm_attn_decode_merged_bf16", "sllm_attn_decode_rope_bf16", "sllm_attn_decode_capped_bf16"):
             getattr(self.lib, n).restype = c_int
         self.lib.sllm_attn_decode_scratch_bytes.restype = c_longlong
         self.lib.sllm_attn_decode_uses_mma.restype = c_int
@@ -621,6 +624,27 @@ class DecodeKernels:
             if tickets.numel() < n_seqs * n_kv:
                 raise KernelError(f"attn_decode tickets hold {tickets.numel()} ints, needs {n_seqs * n_kv}")
             _check(self.lib.sllm_attn_decode_merged_bf16(*head, _ptr(tickets, torch.int32, "tickets"), *tail), "attn_decode")
+
+
+    def uses_tensor_cores(self, n_seqs: int, n_heads: int, n_kv: int, head_dim: int) -> bool:
+        """Whether decode attention of this shape runs on the kernel that puts a group's query heads on the tensor cores
+        (the one that knows capped scores and sinks)."""
+        return bool(self.lib.sllm_attn_decode_uses_mma(c_int(n_seqs), c_int(n_heads), c_int(n_kv), c_int(head_dim))) \
+            and not os.environ.get("SLLM_DECODE_SCALAR")
+
+    def attn_decode_capped(self, q, out, seq_pos0, block_table, kpages, vpages, scratch, tickets, n_seqs, n_heads, n_kv, head_dim,
+                           window, scale, n_split, softcap=None, sink=None):
+        """`attn_decode` with tickets where a score s becomes softcap * tanh(s / softcap) and exp(sink[h]) (float32
+        [n_heads]) joins head h's denominator once; only for shapes `uses_tensor_cores` answers."""
+        need = self.lib.sllm_attn_decode_scratch_bytes(c_int(n_seqs), c_int(n_heads), c_int(head_dim), c_int(n_split))
+        if scratch.numel() * scratch.element_size() < need or tickets.numel() < n_seqs * n_kv:
+            raise KernelError(f"attn_decode_capped scratch holds {scratch.numel() * scratch.element_size()} bytes, needs {need}")
+        _check(self.lib.sllm_attn_decode_capped_bf16(
+            _ptr(q, torch.bfloat16, "q"), c_int(q.shape[1]), _ptr(out, torch.bfloat16, "out"), _ptr(seq_pos0, torch.int32, "seq_pos0"),
+            _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), _ptr(kpages, torch.bfloat16, "kpages"),
+            _ptr(vpages, torch.bfloat16, "vpages"), _ptr(scratch, torch.float32, "scratch"), _ptr(tickets, torch.int32, "tickets"),
+            c_int(n_seqs), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(window or 0), c_float(scale), c_int(n_split),
+            c_float(softcap or 0.0), _ptr(sink, torch.float32, "sink"), _stream()), "attn_decode_capped")
 
 
 class SequenceKernels:

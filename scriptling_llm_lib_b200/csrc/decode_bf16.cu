@@ -366,7 +366,17 @@ struct AttnDecodeArgs {
   const float2* cs;     // [positions][rot/2] (cos, sin)
   int rot, interleaved, write_kv;
   int late;             // no key is asked for before the wait for the kernel in front (for comparisons)
+  // the tensor-core kernel only: softcap > 0 turns a score s into softcap * tanh(s / softcap) before the softmax; sink (or
+  // null) [H]: exp(sink[h]) joins head h's denominator once, where the splits are merged (no key, no value)
+  float softcap;
+  const float* sink;
 };
+
+// the softmax denominator ls (relative to the maximum mn, base 2) once a sink has joined it
+__device__ __forceinline__ float ad_sink_joined(float ls, float mn, const float* sink, int h) {
+  if (sink == nullptr) return ls;
+  return mn == -INFINITY ? 1.0f : ls + exp2f(sink[h] * AD_LOG2E - mn);
+}
 
 // Eight consecutive dims [d0, d0+8) of a head's raw row, rotated for the position whose table row
 // is `csr`, rounded to bfloat16 as the rotary kernel would store them.
@@ -448,7 +458,7 @@ __device__ __forceinline__ void ad_ticket_merge(const AttnDecodeArgs& p, int b, 
           lsum += ls[i] * c;
         }
         lsum = warp_sum(lsum);
-        if (lane == 0) sm_l[r] = lsum;
+        if (lane == 0) sm_l[r] = ad_sink_joined(lsum, mn, p.sink, g * nrep + h0 + r);
       }
       __syncthreads();
       for (int v = threadIdx.x; v < nh * HD; v += AD_WARPS * 32) {
@@ -477,6 +487,7 @@ __device__ __forceinline__ void ad_ticket_merge(const AttnDecodeArgs& p, int b, 
       a += __ldcg(ps + dd) * c;
       ls += __ldcg(ps + HD + 1) * c;
     }
+    ls = ad_sink_joined(ls, mn, p.sink, h);
     p.out[((size_t)b * p.H + h) * HD + dd] = __float2bfloat16_rn(ls > 0.f ? a / ls : 0.f);
   }
 }
@@ -753,6 +764,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_mma_kernel(AttnDeco
   const float2* csr = RAW ? p.cs + (size_t)pos * (p.rot >> 1) : nullptr;
   const uint4 zero = make_uint4(0, 0, 0, 0);
   const float sc = p.scale * AD_LOG2E;
+  const float cap_l2 = p.softcap * AD_LOG2E, cap_in = p.softcap > 0.f ? p.scale / p.softcap : 0.f;
 
   auto fetch = [&](uint4 (&kr)[2][NJ], uint4 (&vr)[4][NC], int base) {
     const size_t row0 = ((size_t)bt[base / SLLM_PAGE] * p.G + g) * SLLM_PAGE + (base % SLLM_PAGE);
@@ -845,7 +857,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_mma_kernel(AttnDeco
 #pragma unroll
         for (int e = 0; e < 4; e++) {
           int key = base + u * 8 + 2 * t + (e & 1);
-          s[u][e] = (key >= k_lo && key < k_hi) ? s[u][e] * sc : -INFINITY;
+          const float sv = p.softcap > 0.f ? cap_l2 * tanhf(s[u][e] * cap_in) : s[u][e] * sc;
+          s[u][e] = (key >= k_lo && key < k_hi) ? sv : -INFINITY;
         }
       }
       float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -953,6 +966,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_mma_kernel(AttnDeco
         ls += sm_ml[w][r][1] * c;
       }
       if (p.n_split == 1 && p.tickets != nullptr) {        // nothing to merge with: this is the result
+        ls = ad_sink_joined(ls, mn, p.sink, g * nrep + r0 + r);
         p.out[((size_t)b * p.H + g * nrep + r0 + r) * HD + dd] = __float2bfloat16_rn(ls > 0.f ? a / ls : 0.f);
         continue;
       }
@@ -967,7 +981,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_mma_kernel(AttnDeco
 
 // out[b, h*HD + d] = sum_s acc_s[d] 2^(m_s - M) / sum_s l_s 2^(m_s - M)
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out, int H, int HD,
-                                         int n_split) {
+                                         int n_split, const float* __restrict__ sink) {
   pdl_launch_dependents();
   pdl_wait();
   int h = blockIdx.x, b = blockIdx.y;
@@ -983,6 +997,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part, bf16* _
       a += ld_dep(ps + dd) * c;
       ls += ld_dep(ps + HD + 1) * c;
     }
+    ls = ad_sink_joined(ls, mn, sink, h);
     out[((size_t)b * H + h) * HD + dd] = __float2bfloat16_rn(ls > 0.f ? a / ls : 0.f);
   }
 }
@@ -1011,9 +1026,10 @@ static int attn_decode_launch(const AttnDecodeArgs& a, bf16* out, int B, cudaStr
 #undef AD_MMA
       if (e != cudaSuccess || a.tickets != nullptr) return (int)e;
       return (int)sllm_launch(attn_decode_merge_kernel, dim3(a.H, B), dim3(HD), 0, stream, (const float*)a.part, out, a.H,
-                              HD, a.n_split);
+                              HD, a.n_split, a.sink);
     }
   }
+  if (a.softcap > 0.f || a.sink != nullptr) return SLLM_ERR_ARG;      // capped scores and sinks: the tensor-core kernel only
   if (a.cs != nullptr) {
     if (nrep % 4 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 4, true, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
     else if (nrep % 2 == 0) e = sllm_launch(attn_decode_split_kernel<HD, 2, true, false>, grid, dim3(AD_WARPS * 32), 0, stream, a);
@@ -1027,7 +1043,7 @@ static int attn_decode_launch(const AttnDecodeArgs& a, bf16* out, int B, cudaStr
   }
   if (e != cudaSuccess || a.tickets != nullptr) return (int)e;
   return (int)sllm_launch(attn_decode_merge_kernel, dim3(a.H, B), dim3(HD < 32 ? 32 : HD), 0, stream,
-                          (const float*)a.part, out, a.H, HD, a.n_split);
+                          (const float*)a.part, out, a.H, HD, a.n_split, (const float*)nullptr);
 }
 
 // Bytes of scratch `part` must have: B * H * n_split * (hd + 2) floats.
@@ -1038,7 +1054,8 @@ SLLM_EXPORT long long sllm_attn_decode_scratch_bytes(int B, int H, int hd, int n
 static int attn_decode_dispatch(const void* q, int q_ld, void* out, const int* seq_pos0, const int* block_table,
                                 int max_pages, const void* kpages, const void* vpages, void* scratch, int* tickets, int B,
                                 int H, int G, int hd, int window, float scale, int n_split, cudaStream_t stream,
-                                const void* cos_sin = nullptr, int rot = 0, int interleaved = 0, int write_kv = 0) {
+                                const void* cos_sin = nullptr, int rot = 0, int interleaved = 0, int write_kv = 0,
+                                float softcap = 0.f, const float* sink = nullptr) {
   if (B <= 0) return 0;
   if (G < 1 || H % G != 0 || n_split < 1 || (q_ld & 7) || ((uintptr_t)q & 15)) return SLLM_ERR_ARG;
   if (cos_sin != nullptr && (rot < 2 || rot > hd || (rot % (interleaved ? 8 : 16)) != 0 || tickets == nullptr)) return SLLM_ERR_ARG;
@@ -1047,6 +1064,8 @@ static int attn_decode_dispatch(const void* q, int q_ld, void* out, const int* s
                    write_kv, 0};
   static const int late = getenv("SLLM_DECODE_LATE_KEYS") != nullptr;   // for comparisons
   a.late = late;
+  a.softcap = softcap;
+  a.sink = sink;
   switch (hd) {
     case 16: return attn_decode_launch<16>(a, (bf16*)out, B, stream);
     case 32: return attn_decode_launch<32>(a, (bf16*)out, B, stream);
@@ -1074,6 +1093,18 @@ SLLM_EXPORT int sllm_attn_decode_merged_bf16(const void* q, int q_ld, void* out,
   if (tickets == nullptr) return SLLM_ERR_ARG;
   return attn_decode_dispatch(q, q_ld, out, seq_pos0, block_table, max_pages, kpages, vpages, scratch, tickets, B, H, G, hd,
                               window, scale, n_split, stream);
+}
+
+// The same with capped scores and a sink per head (either may be off: softcap <= 0, sink null): for shapes the tensor-core
+// kernel serves (sllm_attn_decode_uses_mma); others are refused.
+SLLM_EXPORT int sllm_attn_decode_capped_bf16(const void* q, int q_ld, void* out, const int* seq_pos0,
+                                             const int* block_table, int max_pages, const void* kpages,
+                                             const void* vpages, void* scratch, int* tickets, int B, int H, int G, int hd,
+                                             int window, float scale, int n_split, float softcap, const float* sink,
+                                             cudaStream_t stream) {
+  if (tickets == nullptr || !attn_decode_uses_mma(B, H, G, hd) || getenv("SLLM_DECODE_SCALAR") != nullptr) return SLLM_ERR_ARG;
+  return attn_decode_dispatch(q, q_ld, out, seq_pos0, block_table, max_pages, kpages, vpages, scratch, tickets, B, H, G, hd,
+                              window, scale, n_split, stream, nullptr, 0, 0, 0, softcap, sink);
 }
 
 // Rotary positions, cache write and attention of a decode step in one kernel: `qkv` holds the

@@ -32,8 +32,9 @@ s = (q . k) * scale becomes softcap * tanh(s / softcap) before the softmax. `sin
 whose exponential joins the softmax's denominator; it has no key and no value, is neither scaled nor capped, and
 counts once whatever the number of keys. `gate_per="element"`: the gate matrix is [n_heads * v_dim, hidden] and the
 concatenated heads are multiplied element by element with the sigmoid of its product with the mixer's input
-("head", the default: one logit per head). Capped scores and sinks run on the attention kernels of the generic
-set in both precisions (scores, cap, softmax and sink float32).
+("head", the default: one logit per head). Capped scores and sinks are known to the attention kernels of the generic set
+(both precisions; scores, cap, softmax and sink float32) and, in bfloat16 with heads of 64 or 128, to the tcgen05 prompt
+kernels and to the decode kernel that puts a group's query heads on the tensor cores.
 
 The position encoding is optional (`position=None`: queries and keys as projected). Storing keys
 and values in the cache is this mixer's own step, whatever the encoding: for an encoding that is a
@@ -210,7 +211,21 @@ class Attention(Mixer):
             k = ctx.kernels
             if not qkv.is_contiguous():
                 qkv = qkv.contiguous()
-            if ctx.is_decode and k.attn_decode_split_takes(self.head_dim, qkv.stride(0)):
+            dec = ctx.kernels.decode if x.dtype == torch.bfloat16 else None
+            if (ctx.is_decode and dec is not None and self.head_dim in (64, 128)
+                    and dec.uses_tensor_cores(ctx.n_seqs, self.n_heads, self.n_kv_heads, self.head_dim)):
+                # the decode kernel that puts a group's query heads on the tensor cores knows the cap and the sink
+                n_split = ctx.decode_splits(self.n_heads, self.n_kv_heads, self.head_dim)
+                scratch = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
+                                      device=x.device)
+                dec.attn_decode_capped(qkv, attn, ctx.seq_pos0, block_table, kpages, vpages, scratch,
+                                       ctx.engine.tickets(ctx.n_seqs * self.n_kv_heads), ctx.n_seqs, self.n_heads, self.n_kv_heads,
+                                       self.head_dim, self.span, self.scale, n_split, self.softcap, self.sink)
+            elif not ctx.is_decode and x.dtype == torch.bfloat16 and self.head_dim in PrefillAttentionTC.HEAD_DIMS:
+                ctx.kernels.prefill_attention_tc.attn(qkv, attn, ctx.seq_start, ctx.seq_pos0, block_table, kpages, vpages,
+                                                      ctx.n_seqs, ctx.max_new, self.n_heads, self.n_kv_heads, self.head_dim,
+                                                      self.span, self.scale, ctx.err_flag, self.softcap, self.sink)
+            elif ctx.is_decode and k.attn_decode_split_takes(self.head_dim, qkv.stride(0)):
                 n_split = k.attn_decode_splits(ctx.n_seqs, self.n_heads, self.n_kv_heads, ctx.max_pages, ctx.engine.sm_count)
                 part = torch.empty((ctx.n_seqs * self.n_heads * n_split * (self.head_dim + 2),), dtype=torch.float32,
                                    device=x.device) if n_split > 1 else None

@@ -561,6 +561,58 @@ def test_attention_kernels_with_a_cap_and_a_sink():
                     assert float((out1.cpu().double() - want[L - 1:]).abs().max()) < tol * 5, (H, hd, n_split)
 
 
+@pytest.mark.parametrize("H,G,hd,cap", [(4, 2, 64, 3.0), (8, 1, 64, 4.0), (4, 2, 128, None), (6, 3, 128, 5.0), (3, 3, 128, 2.0), (2, 2, 64, 6.0)])
+def test_the_tensor_core_attention_kernels_with_a_cap_and_a_sink(H, G, hd, cap):
+    """The tcgen05 prompt kernels (a head width each; pairs of heads and pairs of query tiles) and the decode kernel that puts
+    a group's heads on the tensor cores, against the formula on bfloat16-rounded inputs, on pages in scattered order."""
+    from scriptling_llm_lib_b200.csrc.bindings import KernelSet
+    g = torch.Generator().manual_seed(11)
+    ks = KernelSet(torch.bfloat16)
+    L, scale = 330, 2.0 / math.sqrt(hd)
+    q = torch.randn(L, H * hd, generator=g).to(torch.bfloat16)
+    kk = torch.randn(L, G, hd, generator=g).to(torch.bfloat16)
+    vv = torch.randn(L, G, hd, generator=g).to(torch.bfloat16)
+    sink = torch.randn(H, generator=g) * 2.0
+    order = [5, 0, 3, 1, 6, 2]
+    kp = torch.zeros(8, G, 64, hd, dtype=torch.bfloat16)
+    vp = torch.zeros(8, G, 64, hd, dtype=torch.bfloat16)
+    for p in range(L):
+        kp[order[p // 64], :, p % 64] = kk[p]
+        vp[order[p // 64], :, p % 64] = vv[p]
+    rows = [0, 1, 63, 64, 127, 128, 129, 200, 255, 256, 300, L - 1]
+    want = torch.zeros(len(rows), H, hd, dtype=torch.float64)
+    for i, t in enumerate(rows):
+        for h in range(H):
+            s = (kk[:t + 1, h // (H // G)].double() @ q[t, h * hd:(h + 1) * hd].double()) * scale
+            if cap:
+                s = cap * torch.tanh(s / cap)
+            want[i, h] = plain.softmax_with_sink(s, sink[h].double()) @ vv[:t + 1, h // (H // G)].double()
+    want = want.view(len(rows), H * hd)
+    bt = torch.tensor([order], dtype=torch.int32).cuda()
+    kpd, vpd, qd, sd = kp.cuda(), vp.cuda(), q.cuda(), sink.cuda()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.zeros(L, H * hd, dtype=torch.bfloat16, device="cuda")
+    ks.prefill_attention_tc.attn(qd, out, torch.tensor([0, L], dtype=torch.int32).cuda(), torch.tensor([0], dtype=torch.int32).cuda(), bt,
+                                 kpd, vpd, 1, L, H, G, hd, 0, scale, err, cap, sd)
+    assert int(err) == 0
+    assert float((out.cpu().double()[rows] - want).abs().max()) < 2e-2
+    # a portion of 70 rows that lands on a cache of 260
+    out2 = torch.zeros(70, H * hd, dtype=torch.bfloat16, device="cuda")
+    ks.prefill_attention_tc.attn(qd[260:].contiguous(), out2, torch.tensor([0, 70], dtype=torch.int32).cuda(),
+                                 torch.tensor([260], dtype=torch.int32).cuda(), bt, kpd, vpd, 1, 70, H, G, hd, 0, scale, err, cap, sd)
+    assert float((out2.cpu().double()[[40, 69]] - want[[10, 11]]).abs().max()) < 2e-2
+    dec = ks.decode
+    if dec.uses_tensor_cores(1, H, G, hd):
+        for n_split in (1, 3, 6):
+            out1 = torch.zeros(1, H * hd, dtype=torch.bfloat16, device="cuda")
+            scratch = torch.empty(H * n_split * (hd + 2), dtype=torch.float32, device="cuda")
+            tickets = torch.zeros(64, dtype=torch.int32, device="cuda")
+            dec.attn_decode_capped(qd[L - 1:].contiguous(), out1, torch.tensor([L - 1], dtype=torch.int32).cuda(), bt, kpd, vpd, scratch,
+                                   tickets, 1, H, G, hd, 0, scale, n_split, cap, sd)
+            assert float((out1.cpu().double() - want[-1:]).abs().max()) < 2e-2, n_split
+            assert int(tickets.abs().sum()) == 0
+
+
 def test_experts_one_by_one_and_grouped_agree(folders):
     """A step of few rows runs every (token, expert) pair by itself, a longer one groups them by expert."""
     for name, dtype, tol in (("A", "float32", TOL_F32), ("D", "bfloat16", TOL_BF16)):
