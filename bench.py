@@ -1075,6 +1075,144 @@ def gate_kernels_alone(args):
     return 0
 
 
+def tufazen_kernels_alone(args):
+    """What the Tufazen decoder added to the kernels, each alone at TUFAZEN_SIZES[--design-sizes or w2048] beside its like on
+    the same rows: attention with a cap and sinks beside the same kernel without, the sum of several addends beside the sum of
+    one, the normed addend followed by the norm without statistics beside the one followed by an RMS norm, the embedding with
+    a pair table beside the plain one, the gate per element beside the gate per head, the router over all experts beside the
+    one over the picked, the dense clamped gate in the grouped product's epilogue beside the SiLU gate. A prompt of
+    --prefill-tokens rows and a decode step of --batch rows at --context; a JSON line each (CUDA events around a captured run
+    of launches; inputs rotate through more than L2 holds where they are small)."""
+    import torch
+    from types import SimpleNamespace
+    from scriptling_llm_lib_b200.csrc.bindings import KernelSet
+    pk = peaks()
+    z = TUFAZEN_SIZES[(args.design_sizes or "w2048").split(",")[0]]
+    dt, dev, esz = torch.bfloat16, "cuda", 2
+    ks = KernelSet(dt)
+    W, H, G, D, E, top, F = z["width"], z["heads"], z["kv_heads"], z["dim"], z["experts"], z["top"], z["ff"]
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+
+    def timed(launch, n_sets, reps=8):
+        torch.cuda.synchronize()
+        side_stream = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side_stream):
+            for i in range(2):
+                launch(i % n_sets)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side_stream):
+                for i in range(reps):
+                    launch(i % n_sets)
+        for _ in range(2):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(3):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (3 * reps) * 1e3
+
+    def report(name, rows, us, nbytes=None, flops=None, like=None):
+        rec = {"kernel": name, "rows": rows, "us": round(us, 1)}
+        if like is not None:
+            rec["like"] = like
+        if nbytes is not None:
+            rec.update(gbs=round(nbytes / us / 1e3, 1), of_hbm=round(nbytes / us / 1e3 / pk["hbm_gbs"], 3))
+        if flops is not None:
+            rec.update(tflops=round(flops / us / 1e6, 1), of_bf16=round(flops / us / 1e6 / pk["bf16_tflops"], 3))
+        print(json.dumps(rec), flush=True)
+
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    for label, lens, ctxlen in (("prompt", [args.prefill_tokens], args.prefill_tokens), ("decode", [1] * args.batch, args.context)):
+        T, B = sum(lens), len(lens)
+        start = [0]
+        for n in lens:
+            start.append(start[-1] + n)
+        pages = -(-ctxlen // 64)
+        pos0 = torch.zeros(B, dtype=torch.int32, device=dev) if T != B else torch.full((B,), ctxlen - 1, dtype=torch.int32, device=dev)
+        c = SimpleNamespace(
+            seq_start=torch.tensor(start, dtype=torch.int32, device=dev),
+            tok_seq=torch.repeat_interleave(torch.arange(B, dtype=torch.int32, device=dev), torch.tensor(lens, device=dev)).int(),
+            slots=torch.arange(B, dtype=torch.int32, device=dev), n_seqs=B, max_new=max(lens), seq_pos0=pos0, is_decode=T == B,
+            tok_pos=(torch.arange(T, dtype=torch.int32, device=dev) if T != B else pos0.clone()))
+        n_sets = 4 if T > 64 else 24
+        table = torch.arange(B * pages, dtype=torch.int32, device=dev).view(B, pages).contiguous()
+        kp = torch.randn(B * pages + 1, G, 64, D, device=dev).to(dt)
+        vp = torch.randn(B * pages + 1, G, 64, D, device=dev).to(dt)
+        q = torch.randn(T, H * D, device=dev).to(dt)
+        o = torch.empty(T, H * D, dtype=dt, device=dev)
+        sink = torch.zeros(H, device=dev)
+        # ---- attention with capped scores and a sink per head, beside the same kernel without either
+        if T != B:
+            seen = T * (T + 1) // 2
+            for cap, sk, name, like in ((30.0, sink, "cap and sinks", None), (None, None, "plain", "cap and sinks")):
+                us = timed(lambda i: ks.prefill_attention_tc.attn(q, o, c.seq_start, c.seq_pos0, table, kp, vp, B, T, H, G, D, 0, D ** -0.5,
+                                                                  err, cap, sk), 1)
+                report(f"attn_prefill {H}/{G} heads of {D}, {name} ({label})", T, us, flops=4 * H * D * seen, like=like)
+        else:
+            n_split = ks.decode.attention_splits(B, H, G, D, pages, sms)
+            scratch = torch.empty(B * H * n_split * (D + 2), dtype=torch.float32, device=dev)
+            tickets = torch.zeros(B * G, dtype=torch.int32, device=dev)
+            us = timed(lambda i: ks.decode.attn_decode_capped(q, o, c.seq_pos0, table, kp, vp, scratch, tickets, B, H, G, D, 0, D ** -0.5,
+                                                              n_split, 30.0, sink), 1)
+            report(f"attn_decode {H}/{G} heads of {D}, cap and sinks, {n_split} splits ({label})", T, us, nbytes=B * ctxlen * G * 2 * D * esz)
+            us = timed(lambda i: ks.decode.attn_decode(q, o, c.seq_pos0, table, kp, vp, scratch, B, H, G, D, 0, D ** -0.5, n_split,
+                                                       tickets=tickets), 1)
+            report(f"attn_decode {H}/{G} heads of {D}, plain, {n_split} splits ({label})", T, us, nbytes=B * ctxlen * G * 2 * D * esz,
+                   like="cap and sinks")
+        # ---- the stream takes three addends at once, beside one addend
+        xs = [torch.randn(T, W, device=dev) for _ in range(n_sets)]
+        ad = [[torch.randn(2, T, W, device=dev), torch.randn(T, W, device=dev).to(dt), torch.randn(T, W, device=dev)] for _ in range(n_sets)]
+        xb = torch.empty(T, W, dtype=dt, device=dev)
+        us = timed(lambda i: ks.gate.add_list_cast(xs[i], ad[i], xb), n_sets)
+        report(f"add_list_cast, three addends ({label})", T, us, nbytes=T * W * (8 + 8 + esz + 4 + esz))
+        us = timed(lambda i: ks.gate.add_cast(xs[i], ad[i][0], xb), n_sets)
+        report(f"add_cast, one addend in two parts ({label})", T, us, nbytes=T * W * (8 + 8 + esz), like="add_list_cast")
+        # ---- x += y / rms(y) w (+ a row vector), then the norm without statistics; beside the same followed by an RMS norm
+        w1, w2, b2, vec = (torch.randn(W, device=dev) for _ in range(4))
+        out = torch.empty(T, W, dtype=dt, device=dev)
+        us = timed(lambda i: ks.gate.add_rms_normed(xs[i], ad[i][0], w1, 1e-6, vec=vec, dyt=(w2, b2, 0.8, out)), n_sets)
+        report(f"add_rms_normed + row vector + tanh norm ({label})", T, us, nbytes=T * W * (8 + 8 + esz))
+        us = timed(lambda i: ks.gate.add_rms_normed(xs[i], ad[i][0], w1, 1e-6, norm=(w2, 1e-6, out)), n_sets)
+        report(f"add_rms_normed + RMS norm ({label})", T, us, nbytes=T * W * (8 + 8 + esz), like="add_rms_normed + tanh norm")
+        # ---- the embedding with a pair table, beside the plain one
+        tab, ptab = torch.randn(DESIGN_VOCAB, W, device=dev).to(dt), torch.randn(100004, W, device=dev).to(dt)
+        tok = torch.randint(0, DESIGN_VOCAB, (T,), dtype=torch.int32, device=dev)
+        last = torch.zeros(B + 1, dtype=torch.int32, device=dev)
+        us = timed(lambda i: ks.embed_pair_rows(tok, c, tab, ptab, 100003, 1009, 31, last, xs[i], err), n_sets)
+        report(f"embed_pair_rows ({label})", T, us, nbytes=T * W * (2 * esz + 4))
+        us = timed(lambda i: ks.embed_rows(tok, tab, xs[i], err), n_sets)
+        report(f"embed_rows ({label})", T, us, nbytes=T * W * (esz + 4), like="embed_pair_rows")
+        # ---- the gate per element, beside the gate per head
+        gl = [torch.randn(T, H * D, device=dev).to(dt) for _ in range(n_sets)]
+        us = timed(lambda i: ks.gate.head_gate(o, gl[i], H * D, 1), n_sets)
+        report(f"head_gate per element ({label})", T, us, nbytes=3 * T * H * D * esz)
+        us = timed(lambda i: ks.gate.head_gate(o, gl[i][:, :H], H, D), n_sets)
+        report(f"head_gate per head ({label})", T, us, nbytes=2 * T * H * D * esz, like="per element")
+        # ---- the router: softmax over all experts and groups rated by their best, beside the softmax over the picked
+        zl = torch.randn(T, E, device=dev)
+        idx = torch.empty(T, top, dtype=torch.int32, device=dev)
+        wgt = torch.empty(T, top, device=dev)
+        us = timed(lambda i: ks.mix.moe_route(zl, None, idx, wgt, z["n_groups"], z["keep"], top, 1.0, router="grouped_softmax"), 1)
+        report(f"moe_route grouped_softmax, {top} of {E} in {z['n_groups']} groups ({label})", T, us)
+        us = timed(lambda i: ks.mix.moe_route(zl, None, idx, wgt, 1, 1, top, 1.0, router="top_softmax"), 1)
+        report(f"moe_route top_softmax, {top} of {E} ({label})", T, us, like="grouped_softmax")
+        # ---- the dense feed-forward's first product with the clamped gate in its epilogue, beside the SiLU gate of the plain product
+        if T > 128:
+            xin = torch.randn(T, W, device=dev).to(dt)
+            wgu = (torch.randn(2 * F, W, device=dev) * 0.02).to(dt)
+            hid = torch.empty(T, F, dtype=dt, device=dev)
+            group = torch.zeros(-(-T // 128), dtype=torch.int32, device=dev)
+            us = timed(lambda i: ks.tensor_core.gemm_grouped(xin, wgu.unsqueeze(0), hid, group, err, glu=(7.0, 1.702)), 1)
+            report(f"gate|up product with the clamped gate, {2 * F} x {W} ({label})", T, us, flops=4 * T * F * W)
+            us = timed(lambda i: ks.tensor_core.gemm(xin, wgu, hid, err, swiglu=True), 1)
+            report(f"gate|up product with the SiLU gate, {2 * F} x {W} ({label})", T, us, flops=4 * T * F * W, like="clamped gate")
+    return 0
+
+
 def kernel_alone(args):
     """One decode kernel by itself, as profiles/ quotes it: launched back to back in a CUDA graph over
     inputs that rotate through more bytes than L2 holds, timed with CUDA events; one JSON line per case.
@@ -1181,12 +1319,15 @@ def main():
     ap.add_argument("--no-shapes", dest="shapes", action="store_false", help="skip the Llama-3.2-1B and Llama-3.1-8B sizes")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
                     help="run one part only (a small case to profile); the JSON line then holds that part alone")
-    ap.add_argument("--kernel", default=None, choices=["attn_decode", "gemm_small_m", "sequence", "mix", "gate"],
+    ap.add_argument("--kernel", default=None, choices=["attn_decode", "gemm_small_m", "sequence", "mix", "gate", "tufazen"],
                     help="time one decode kernel alone at --shape, --batch (and --context) instead of the model; 'sequence': "
                          "the kernels of the mixers with state at --design-sizes, for a prompt and for a decode step; 'mix': "
                          "the same for the kernels of latent attention, decayed linear attention, the selective scan and "
                          "routed experts; 'gate': the same for the kernels of the Belasun decoder's layers (convolution behind "
-                         "the projections, whole-projection norm, gate per head, chunked attention, gated experts, token input)")
+                         "the projections, whole-projection norm, gate per head, chunked attention, gated experts, token input); 'tufazen': "
+                         "what the Tufazen decoder added (capped attention with sinks, sums of several addends, the normed addend "
+                         "before a tanh norm, the pair-table embedding, the gate per element, the router over groups, the dense "
+                         "clamped gate), each beside its like")
     ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="measure this design's prompt step and decoding at a few real layer sizes beside the Llama decoder "
                          "of equal size (--prefill-tokens, --batch, --context, --steps, --dtype, --only apply) instead of the "
@@ -1207,6 +1348,8 @@ def main():
         return gate_kernels_alone(args)
     if args.kernel == "mix":
         return mix_kernels_alone(args)
+    if args.kernel == "tufazen":
+        return tufazen_kernels_alone(args)
     if args.kernel is not None:
         return kernel_alone(args)
     if args.design is not None:

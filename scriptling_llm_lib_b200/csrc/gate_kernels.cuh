@@ -340,6 +340,20 @@ __global__ void head_gate_vec_kernel(A* __restrict__ o, int ldo, const void* __r
   st4(p, make_float4(v.x * s, v.y * s, v.z * s, v.w * s));
 }
 
+// a logit per element (vd == 1), eight neighbouring columns a thread: o[t][j] *= sigmoid(g[t][j]), g of the element type;
+// n, ldo, ldg multiples of eight, both aligned for the wide access
+template <typename A>
+__global__ void elem_gate_vec8_kernel(A* __restrict__ o, int ldo, const A* __restrict__ g, int ldg, int T, int n) {
+  size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= (size_t)T * n) return;
+  int t = (int)(i / n), r = (int)(i % n);
+  A* p = o + (size_t)t * ldo + r;
+  F8 v = ld8(p), w = ld8(g + (size_t)t * ldg + r);
+#pragma unroll
+  for (int k = 0; k < 8; k++) v.f[k] *= sigmoid_f(w.f[k]);
+  st8(p, v);
+}
+
 // ------------------------------------------------------------------ the stream takes its pending addend; a copy in A
 // x float [n] += sum over p < P of d[p * n + i] (d float or A; P == 0: nothing to add); xb[i] = A(x[i]).
 template <typename A>

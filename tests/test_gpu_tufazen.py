@@ -466,6 +466,10 @@ def test_the_small_kernels_against_their_formulas():
         od = o.clone().cuda()
         ks.gate.head_gate(od, lg.cuda(), 15, 1)
         assert float((od.cpu().double() - o.double() * torch.sigmoid(lg.double())).abs().max()) < tol
+        o, wide = torch.randn(7, 32, generator=g).to(dtype), torch.randn(7, 48, generator=g).to(dtype).cuda()     # eight columns a thread
+        od = o.clone().cuda()
+        ks.gate.head_gate(od, wide[:, 16:], 32, 1)
+        assert float((od.cpu().double() - o.double() * torch.sigmoid(wide[:, 16:].cpu().double())).abs().max()) < tol
         # several addends and a row vector in one pass; the rounded copy
         for T, d in ((5, 72), (6, 50)):
             x = torch.randn(T, d, generator=g)
