@@ -572,18 +572,18 @@ def test_the_tensor_core_attention_kernels_with_a_cap_and_a_sink(H, G, hd, cap):
     from scriptling_llm_lib_b200.csrc.bindings import KernelSet
     g = torch.Generator().manual_seed(11)
     ks = KernelSet(torch.bfloat16)
-    L, scale = 330, 2.0 / math.sqrt(hd)
+    L, scale = 800, 2.0 / math.sqrt(hd)
     q = torch.randn(L, H * hd, generator=g).to(torch.bfloat16)
     kk = torch.randn(L, G, hd, generator=g).to(torch.bfloat16)
     vv = torch.randn(L, G, hd, generator=g).to(torch.bfloat16)
     sink = torch.randn(H, generator=g) * 2.0
-    order = [5, 0, 3, 1, 6, 2]
-    kp = torch.zeros(8, G, 64, hd, dtype=torch.bfloat16)
-    vp = torch.zeros(8, G, 64, hd, dtype=torch.bfloat16)
+    order = [5, 0, 3, 1, 6, 2, 12, 9, 7, 13, 4, 8, 10]
+    kp = torch.zeros(14, G, 64, hd, dtype=torch.bfloat16)
+    vp = torch.zeros(14, G, 64, hd, dtype=torch.bfloat16)
     for p in range(L):
         kp[order[p // 64], :, p % 64] = kk[p]
         vp[order[p // 64], :, p % 64] = vv[p]
-    rows = [0, 1, 63, 64, 127, 128, 129, 200, 255, 256, 300, L - 1]
+    rows = [0, 1, 63, 64, 127, 128, 129, 200, 255, 256, 300, 511, 640, L - 2, L - 1]
     want = torch.zeros(len(rows), H, hd, dtype=torch.float64)
     for i, t in enumerate(rows):
         for h in range(H):
@@ -600,14 +600,14 @@ def test_the_tensor_core_attention_kernels_with_a_cap_and_a_sink(H, G, hd, cap):
                                  kpd, vpd, 1, L, H, G, hd, 0, scale, err, cap, sd)
     assert int(err) == 0
     assert float((out.cpu().double()[rows] - want).abs().max()) < 2e-2
-    # a portion of 70 rows that lands on a cache of 260
-    out2 = torch.zeros(70, H * hd, dtype=torch.bfloat16, device="cuda")
-    ks.prefill_attention_tc.attn(qd[260:].contiguous(), out2, torch.tensor([0, 70], dtype=torch.int32).cuda(),
-                                 torch.tensor([260], dtype=torch.int32).cuda(), bt, kpd, vpd, 1, 70, H, G, hd, 0, scale, err, cap, sd)
-    assert float((out2.cpu().double()[[40, 69]] - want[[10, 11]]).abs().max()) < 2e-2
+    # a portion of 160 rows that lands on a cache of 640
+    out2 = torch.zeros(160, H * hd, dtype=torch.bfloat16, device="cuda")
+    ks.prefill_attention_tc.attn(qd[640:].contiguous(), out2, torch.tensor([0, 160], dtype=torch.int32).cuda(),
+                                 torch.tensor([640], dtype=torch.int32).cuda(), bt, kpd, vpd, 1, 160, H, G, hd, 0, scale, err, cap, sd)
+    assert float((out2.cpu().double()[[0, 158, 159]] - want[[12, 13, 14]]).abs().max()) < 2e-2
     dec = ks.decode
     if dec.uses_tensor_cores(1, H, G, hd):
-        for n_split in (1, 3, 6):
+        for n_split in (1, 3, 6, 12):                 # more than eight splits are merged a warp a head
             out1 = torch.zeros(1, H * hd, dtype=torch.bfloat16, device="cuda")
             scratch = torch.empty(H * n_split * (hd + 2), dtype=torch.float32, device="cuda")
             tickets = torch.zeros(64, dtype=torch.int32, device="cuda")
