@@ -241,6 +241,13 @@ class KernelSet:
         return self._fa_tc
 
     @property
+    def prefill_attention_mma(self) -> "PrefillAttentionMMA":
+        k = self.__dict__.get("_prefill_mma")
+        if k is None:
+            k = self.__dict__["_prefill_mma"] = PrefillAttentionMMA()
+        return k
+
+    @property
     def seq(self) -> "SequenceKernels":
         """The kernels of mixers with state along the sequence, for this set's element type."""
         if getattr(self, "_seq", None) is None:
@@ -465,6 +472,36 @@ class PrefillAttentionTC:
             c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(window or 0), c_float(scale),
             c_float(softcap or 0.0), _ptr(sink, torch.float32, "sink"), _ptr(err_flag, torch.int32, "err_flag"), _stream()),
             "attn_prefill_tc")
+
+
+class PrefillAttentionMMA:
+    """Causal attention of a prompt step on mma.sync for key and value widths the tcgen05 kernels do not take (bfloat16): keys
+    of 64, 96, 128, 192 or 256, values of 64 or 128; rows in storage may be wider than what is used."""
+    KEY_WIDTHS = (64, 96, 128, 192, 256)
+    VALUE_WIDTHS = (64, 128)
+
+    def __init__(self):
+        self.lib = load_library("attn_prefill_mma")
+        self.lib.sllm_attn_prefill_mma_bf16.restype = c_int
+
+    @classmethod
+    def widths_for(cls, key_dim: int, value_dim: int):
+        """The (key width, value width) the kernel would run for heads of these widths (padded with zeros), or None."""
+        k = next((w for w in cls.KEY_WIDTHS if w >= key_dim), None)
+        v = next((w for w in cls.VALUE_WIDTHS if w >= value_dim), None)
+        return None if k is None or v is None else (k, v)
+
+    def attn(self, q, q_hw, out, o_hw, seq_start, seq_pos0, block_table, kpages, vpages, n_seqs, max_new, n_heads, n_kv, kd, vd,
+             window, scale, softcap=None, sink=None):
+        """q [T, n_heads * q_hw], out [T, n_heads * o_hw] (the o_hw - vd columns past a head's values are set to 0), kpages
+        [pages, n_kv, 64, k_w], vpages [pages, n_kv, 64, v_w]; kd and vd are the widths used."""
+        _check(self.lib.sllm_attn_prefill_mma_bf16(
+            _ptr(q, torch.bfloat16, "q"), c_int(q.shape[1]), c_int(q_hw), _ptr(out, torch.bfloat16, "out"), c_int(out.shape[1]),
+            c_int(o_hw), _ptr(seq_start, torch.int32, "seq_start"), _ptr(seq_pos0, torch.int32, "seq_pos0"),
+            _ptr(block_table, torch.int32, "block_table"), c_int(block_table.shape[1]), _ptr(kpages, torch.bfloat16, "kpages"),
+            c_int(kpages.shape[-1]), _ptr(vpages, torch.bfloat16, "vpages"), c_int(vpages.shape[-1]), c_int(n_seqs), c_int(max_new),
+            c_int(n_heads), c_int(n_kv), c_int(kd), c_int(vd), c_int(window or 0), c_float(scale), c_float(softcap or 0.0),
+            _ptr(sink, torch.float32, "sink"), _stream()), "attn_prefill_mma")
 
 
 class DecodeKernels:

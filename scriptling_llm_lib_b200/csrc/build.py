@@ -34,6 +34,7 @@ LIBRARIES: dict[str, tuple[str, tuple[str, ...]]] = {
     "decode_bf16": ("decode_bf16.cu", ("common.cuh", "attn_decode_noalloc.h")),
     "gemm_tcgen05": ("gemm_tcgen05.cu", ("common.cuh", "tcgen05.cuh")),
     "attn_prefill_tcgen05": ("attn_prefill_tcgen05.cu", ("common.cuh", "tcgen05.cuh")),
+    "attn_prefill_mma": ("attn_prefill_mma.cu", ("common.cuh",)),
     "seq_f32": ("lib_seq_f32.cu", ("common.cuh", "sequence_kernels.cuh", "sequence_launchers.inc")),
     "seq_bf16": ("lib_seq_bf16.cu", ("common.cuh", "sequence_kernels.cuh", "sequence_launchers.inc")),
     "mix_f32": ("lib_mix_f32.cu", ("common.cuh", "mix_kernels.cuh", "mix_launchers.inc")),

@@ -59,7 +59,7 @@ def _mixer(cfg: TufazenConfig, layer, p: str) -> PartSpec:
         hidden=cfg.width, n_heads=m.heads, dim=m.dim, rot_dim=m.rot_dim, v_dim=m.vdim, kv_rank=m.kv_rank, scale=m.scale,
         position=_rotary(m.rot, m.rot_dim, "half"), norm_eps=cfg.norm_eps, q_name=None, q_rank=m.q_rank, dq_name=p + "dq",
         dq_norm_name=p + "dq.norm", uq_name=p + "uq", uk_name=p + "uk", uv_name=p + "uv", o_name=p + "o", dkv_name=p + "dkv",
-        dkv_norm_name=p + "dkv.norm", gate_name=p + "g"))
+        dkv_norm_name=p + "dkv.norm", gate_name=p + "g", prompt_kernel="tensor"))
 
 
 def _feed_forward(cfg: TufazenConfig, f, p: str) -> PartSpec:

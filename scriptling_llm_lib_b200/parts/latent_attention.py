@@ -24,6 +24,9 @@ Three options. `q_rank`: the queries go through a latent of their own, c_q = (Wd
 down-projection leaves float32 sums, the norm is float32, and `q_name` is not used). `pairing="half"`: the rotated part
 turns dim i with dim i + rot / 2 instead of neighbours. `gate_name`: a matrix [n_heads, hidden] on the mixer's input; head
 i's output is multiplied by the sigmoid of its logit before Wo (the logits ride in the down-projection's product).
+`prompt_kernel="tensor"`: in bfloat16 the per-head form of a prompt runs on the mma.sync attention kernel that takes keys and
+values of different widths (rows padded with zeros to the widths it is built for) instead of the float32 tiled kernel; the
+weights then enter the product with the values rounded to bfloat16.
 
 The products run in the engine's dtype and the cache holds it; the latent's norm, the rotation,
 the absorbed queries, scores, softmax and sums over the latent are float32.
@@ -46,7 +49,7 @@ class LatentAttention(Mixer):
                  position: PartSpec | None, norm_eps: float, q_name: str | None, uk_name: str, uv_name: str, o_name: str,
                  dkv_name: str | None = None, dkv_norm_name: str | None = None, shares_cache: bool = False,
                  q_rank: int | None = None, dq_name: str | None = None, dq_norm_name: str | None = None, uq_name: str | None = None,
-                 gate_name: str | None = None):
+                 gate_name: str | None = None, prompt_kernel: str = "float32"):
         if kv_rank < 1 or kv_rank > self.MAX_RANK:
             raise ValueError(f"latent of width {kv_rank}: the attention kernel takes 1..{self.MAX_RANK}")
         if not shares_cache and (dkv_name is None or dkv_norm_name is None):
@@ -77,7 +80,11 @@ class LatentAttention(Mixer):
         self.proj = Linear(names, widths, hidden) if names else None
         self.out = Linear([o_name], [hidden], n_heads * v_dim)
         self.kv_up = Linear([uk_name, uv_name], [n_heads * dim, n_heads * v_dim], kv_rank)
+        if prompt_kernel not in ("float32", "tensor"):
+            raise ValueError(f"prompt kernel {prompt_kernel!r}; known: float32, tensor")
+        self.prompt_kernel = prompt_kernel
         self.hd = (max(dim + rot_dim, v_dim) + 3) // 4 * 4      # one width for keys, values and queries of the per-head form
+        self.mma = None                                         # (key width, value width) of the tensor-core prompt kernel, once bound
         self.uk_name, self.uv_name, self.dkv_norm_name = uk_name, uv_name, dkv_norm_name
 
     def tensor_specs(self):
@@ -100,6 +107,11 @@ class LatentAttention(Mixer):
         self.out.bind(tensors, dtype, device)
         self.wuk, self.wuv = tensors[self.uk_name], tensors[self.uv_name]
         self.kv_up.bind(tensors, dtype, device)
+        if self.prompt_kernel == "tensor" and dtype == torch.bfloat16:
+            from ..csrc.bindings import PrefillAttentionMMA
+            self.mma = PrefillAttentionMMA.widths_for(self.D + self.P, self.V)
+            if self.mma is not None:                            # rows padded with zeros up to the widths that kernel is built for
+                self.hd = max(self.mma)
         # the output matrix with zero columns where the per-head form pads a head's values to `hd`
         if self.hd != self.V:
             w = self.out.weight
@@ -166,8 +178,12 @@ class LatentAttention(Mixer):
         qt = torch.empty((T, self.H * self.hd), dtype=q.dtype, device=dev)
         k.latent_heads(q, kv, dense, self.R, ctx, table, kt, vt, qt, self.H, self.D, self.P, self.V, self.hd)
         attn = torch.empty((T, self.H * self.hd), dtype=q.dtype, device=dev)
-        ctx.kernels.attn_paged(qt, attn, ctx.seq_start, ctx.seq_pos0, table, kt, vt, ctx.n_seqs, ctx.max_new, self.H, self.H,
-                               self.hd, None, self.scale)
+        if self.mma is not None:
+            ctx.kernels.prefill_attention_mma.attn(qt, self.hd, attn, self.hd, ctx.seq_start, ctx.seq_pos0, table, kt, vt, ctx.n_seqs,
+                                                   ctx.max_new, self.H, self.H, self.mma[0], self.mma[1], None, self.scale)
+        else:
+            ctx.kernels.attn_paged(qt, attn, ctx.seq_start, ctx.seq_pos0, table, kt, vt, ctx.n_seqs, ctx.max_new, self.H, self.H,
+                                   self.hd, None, self.scale)
         return self._finish(attn, gate, self.hd, self.out_wide, ctx)
 
     def forward(self, x, ctx, unit, writes):

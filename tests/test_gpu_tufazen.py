@@ -617,6 +617,54 @@ def test_the_tensor_core_attention_kernels_with_a_cap_and_a_sink(H, G, hd, cap):
             assert int(tickets.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("H,G,kd,vd,width,cap,sinks", [(4, 2, 96, 64, 96, None, False), (3, 3, 192, 128, 192, None, False),
+                                                         (2, 1, 64, 64, 64, 4.0, True), (2, 2, 256, 128, 256, 8.0, True),
+                                                         (5, 5, 128, 64, 136, None, True)])
+def test_the_prompt_attention_kernel_for_keys_and_values_of_different_widths(H, G, kd, vd, width, cap, sinks):
+    """The mma.sync prompt kernel against the formula: rows in storage `width` wide of which the keys use kd and the values
+    vd, pages in scattered order, a whole prompt and a portion that lands on a cache."""
+    from scriptling_llm_lib_b200.csrc.bindings import KernelSet
+    g = torch.Generator().manual_seed(12)
+    ks = KernelSet(torch.bfloat16)
+    L, scale = 420, 2.0 / math.sqrt(kd)
+    q = torch.zeros(L, H, width)
+    q[:, :, :kd] = torch.randn(L, H, kd, generator=g)
+    kk, vv = torch.zeros(L, G, width), torch.zeros(L, G, width)
+    kk[:, :, :kd] = torch.randn(L, G, kd, generator=g)
+    vv[:, :, :vd] = torch.randn(L, G, vd, generator=g)
+    vv[:, :, vd:] = 7.0                                     # columns past the values used are not read
+    q, kk, vv = q.to(torch.bfloat16), kk.to(torch.bfloat16), vv.to(torch.bfloat16)
+    sink = torch.randn(H, generator=g) * 2.0 if sinks else None
+    order = [5, 0, 3, 1, 6, 2, 4]
+    kp = torch.full((8, G, 64, width), float("nan"), dtype=torch.bfloat16)      # what a page held before must not show
+    vp = torch.full((8, G, 64, width), float("nan"), dtype=torch.bfloat16)
+    for p in range(L):
+        kp[order[p // 64], :, p % 64] = kk[p]
+        vp[order[p // 64], :, p % 64] = vv[p]
+    rows = [0, 1, 15, 16, 63, 64, 65, 127, 128, 200, 300, 383, 384, L - 1]
+    want = torch.zeros(len(rows), H, vd, dtype=torch.float64)
+    for i, t in enumerate(rows):
+        for h in range(H):
+            s = (kk[:t + 1, h // (H // G)].double() @ q[t, h].double()) * scale
+            if cap:
+                s = cap * torch.tanh(s / cap)
+            want[i, h] = plain.softmax_with_sink(s, sink[h].double() if sinks else None) @ vv[:t + 1, h // (H // G), :vd].double()
+    bt = torch.tensor([order], dtype=torch.int32).cuda()
+    kpd, vpd, qd = kp.cuda(), vp.cuda(), q.view(L, H * width).cuda()
+    sd = sink.cuda() if sinks else None
+    out = torch.full((L, H * width), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ks.prefill_attention_mma.attn(qd, width, out, width, torch.tensor([0, L], dtype=torch.int32).cuda(),
+                                  torch.tensor([0], dtype=torch.int32).cuda(), bt, kpd, vpd, 1, L, H, G, kd, vd, 0, scale, cap, sd)
+    got = out.cpu().double().view(L, H, width)
+    assert float((got[rows][:, :, :vd] - want).abs().max()) < 2e-2
+    assert float(got[:, :, vd:].abs().max()) == 0.0 if width > vd else True
+    out2 = torch.zeros(100, H * width, dtype=torch.bfloat16, device="cuda")
+    ks.prefill_attention_mma.attn(qd[320:].contiguous(), width, out2, width, torch.tensor([0, 100], dtype=torch.int32).cuda(),
+                                  torch.tensor([320], dtype=torch.int32).cuda(), bt, kpd, vpd, 1, 100, H, G, kd, vd, 0, scale, cap, sd)
+    got2 = out2.cpu().double().view(100, H, width)
+    assert float((got2[[63, 64, 99]][:, :, :vd] - want[[11, 12, 13]]).abs().max()) < 2e-2
+
+
 def test_experts_one_by_one_and_grouped_agree(folders):
     """A step of few rows runs every (token, expert) pair by itself, a longer one groups them by expert."""
     for name, dtype, tol in (("A", "float32", TOL_F32), ("D", "bfloat16", TOL_BF16)):
