@@ -1163,6 +1163,22 @@ def tufazen_kernels_alone(args):
                                                        tickets=tickets), 1)
             report(f"attn_decode {H}/{G} heads of {D}, plain, {n_split} splits ({label})", T, us, nbytes=B * ctxlen * G * 2 * D * esz,
                    like="cap and sinks")
+        # ---- a latent layer's prompt from position 0, keys and values formed per head (192 and 128 wide): the mma.sync kernel for
+        # unequal widths beside the float32 tiled kernel on the same rows
+        if T != B:
+            hw = z["dim"] + z["rot_dim"]
+            widths = ks.prefill_attention_mma.widths_for(hw, z["vdim"])
+            if widths is not None:
+                hd = max(widths)
+                kt = torch.randn(B * pages + 1, H, 64, hd, device=dev).to(dt)
+                qt = torch.randn(T, H * hd, device=dev).to(dt)
+                ot = torch.empty(T, H * hd, dtype=dt, device=dev)
+                flops = 2 * H * (hw + z["vdim"]) * (T * (T + 1) // 2)
+                us = timed(lambda i: ks.prefill_attention_mma.attn(qt, hd, ot, hd, c.seq_start, c.seq_pos0, table, kt, kt, B, T, H, H,
+                                                                   widths[0], widths[1], 0, hw ** -0.5), 1)
+                report(f"attn_prefill_mma {H} heads, keys {widths[0]}, values {widths[1]} ({label})", T, us, flops=flops)
+                us = timed(lambda i: ks.attn_paged(qt, ot, c.seq_start, c.seq_pos0, table, kt, kt, B, T, H, H, hd, None, hw ** -0.5), 1)
+                report(f"attn_paged {H} heads of {hd}, float32 tiles ({label})", T, us, flops=flops, like="attn_prefill_mma")
         # ---- the stream takes three addends at once, beside one addend
         xs = [torch.randn(T, W, device=dev) for _ in range(n_sets)]
         ad = [[torch.randn(2, T, W, device=dev), torch.randn(T, W, device=dev).to(dt), torch.randn(T, W, device=dev)] for _ in range(n_sets)]
