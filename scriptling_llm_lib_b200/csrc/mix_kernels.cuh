@@ -713,10 +713,49 @@ __global__ void __launch_bounds__(256) latent_attn_vec_kernel(const float* __res
 }
 
 // merge: olat[t][h] = sum_s w_s acc_s / sum_s w_s l_s, w_s = exp(m_s - max m): the splits' sums over the latent as one
-// normalised vector [R] per (row, head).
-__global__ void latent_merge_kernel(const float* __restrict__ part, float* __restrict__ olat, int R, int n_split) {
+// normalised vector [R] per (row, head). The first warp weighs the splits once (a lane takes splits lane, lane + 32, ...),
+// then every thread adds its columns over the splits with loads that do not depend on one another.
+#define MIX_MERGE_SPLITS 64
+__global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ part, float* __restrict__ olat, int R, int n_split) {
+  __shared__ float w[MIX_MERGE_SPLITS];
+  __shared__ float s_inv;
   size_t item = blockIdx.x;                       // t * H + h
   const float* p0 = part + item * n_split * (R + 2);
+  if (n_split <= MIX_MERGE_SPLITS) {
+    if (threadIdx.x < 32) {
+      const int lane = threadIdx.x;
+      float ms[MIX_MERGE_SPLITS / 32], ls[MIX_MERGE_SPLITS / 32], mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < MIX_MERGE_SPLITS / 32; i++) {
+        int s2 = lane + 32 * i;
+        ms[i] = s2 < n_split ? p0[(size_t)s2 * (R + 2)] : -INFINITY;
+        ls[i] = s2 < n_split ? p0[(size_t)s2 * (R + 2) + 1] : 0.f;
+        mx = fmaxf(mx, ms[i]);
+      }
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float den = 0.f;
+#pragma unroll
+      for (int i = 0; i < MIX_MERGE_SPLITS / 32; i++) {
+        float ws = ms[i] > -INFINITY ? expf(ms[i] - mx) : 0.f;
+        w[lane + 32 * i] = ws;
+        den += ws * ls[i];
+      }
+      for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+      if (lane == 0) s_inv = 1.0f / den;
+    }
+    __syncthreads();
+    const float inv = s_inv;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+      float a = 0.f;
+#pragma unroll 8
+      for (int s = 0; s < n_split; s++) {
+        const float ws = w[s];                    // a split without keys left its sums unwritten: they are not read
+        if (ws != 0.f) a += ws * p0[(size_t)s * (R + 2) + 2 + c];
+      }
+      olat[item * R + c] = a * inv;
+    }
+    return;
+  }
   float mx = -INFINITY;
   for (int s = 0; s < n_split; s++) mx = fmaxf(mx, p0[(size_t)s * (R + 2)]);
   float den = 0.f;
