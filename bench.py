@@ -545,14 +545,14 @@ TUFAZEN_SIZES = {
 def tufazen_config(z):
     att = {"type": "attention", "mlp": {"ff": z["ff"], "kind": "dense", "limit": 7.0}, "mixer": {
         "dim": z["dim"], "heads": z["heads"], "kv_heads": z["kv_heads"], "scale": z["dim"] ** -0.5, "softcap": 30.0, "vdim": z["dim"],
-        "rot": {"base": 10000.0, "dims": z["dim"] // 2, "scaling": {"factor": 8.0, "fast": 32.0, "original": 4096, "slow": 1.0}}}}
+        "rot": {"base": 10000.0, "dims": z["dim"] // 2, "scaling": {"factor": 4.0, "fast": 16.0, "original": 8192, "slow": 2.0}}}}
     lat = {"type": "latent_attention", "mixer": {
         "dim": z["dim"], "heads": z["heads"], "kv_rank": z["rank"], "q_rank": z["q_rank"], "rot_dim": z["rot_dim"],
         "rot": {"base": 10000.0, "dims": z["rot_dim"]}, "scale": (z["dim"] + z["rot_dim"]) ** -0.5, "vdim": z["vdim"]},
         "mlp": {"expert": {"ff": z["expert_ff"]}, "kind": "moe", "shared": {"ff": z["shared_ff"]}, "router": {
             "experts": z["experts"], "groups": {"count": z["n_groups"], "keep": z["keep"]}, "top": z["top"]}}}
     return {"architecture": "Tufazen", "embedding": {"bigram": {"buckets": 100003, "mul_cur": 31, "mul_prev": 1009}},
-            "layers": [att, lat, att, lat], "logit_scale": 0.5, "loop": {"start": 0, "stop": 2, "times": 2}, "norm": {"eps": 1e-6},
+            "layers": [att, lat, att, lat], "logit_scale": 0.25, "loop": {"start": 0, "stop": 2, "times": 2}, "norm": {"eps": 1e-6},
             "token_side": {"dim": z["side"]}, "vocab": DESIGN_VOCAB, "width": z["width"]}
 
 

@@ -5,8 +5,8 @@ The file is nested like the other in-house families': `layers` lists the layers,
 the mixer's sizes and constants under `mixer`, and its feed-forward under `mlp` (null: none; `kind` dense or moe).
 Model-wide: `vocab`, `width`, `norm.eps`, `logit_scale` (absent: 1), `embedding.bigram` (`buckets`, `mul_prev`,
 `mul_cur`; absent: a plain embedding), `token_side.dim` (absent: the layers take no input from the token itself) and
-`loop` (`start`, `stop`, `times`: layers start .. stop - 1 run `times` times in a row with the same weights; absent:
-every layer once). Every layer states its own sizes, so two layers of a model may differ in all of them.
+`loop` (`start`, `stop`, `times`: the model goes through the run of layers from `start` up to, not including, `stop`
+that many times on one set of weights before it goes on; absent: every layer once). Every layer states its own sizes, so two layers of a model may differ in all of them.
 
 An `attention` mixer: `heads`, `kv_heads`, `dim` (query/key width of a head), `vdim` (value width; the values are the
 keys, so it equals `dim`), `scale` (multiplies q . k), `softcap` (absent: scores as they are), `rot` (`dims` leading dims

@@ -58,8 +58,9 @@ def sequential_schedule(n_layers: int) -> tuple[ScheduleEntry, ...]:
 
 
 def looped_schedule(n_layers: int, start: int, stop: int, times: int, before_pass=None) -> tuple[ScheduleEntry, ...]:
-    """Layers 0 .. start - 1 once, layers start .. stop - 1 `times` times in a row with the same weights, then the rest once.
-    Every appearance of a layer has a cache unit of its own, numbered in running order. `before_pass(t)` -> the stream
+    """The schedule of a model that goes through the run of layers [start, stop) `times` times on one set of weights: the
+    layers before the run once, the run again and again, then the layers behind it once. Every appearance of a layer has a
+    cache unit of its own, numbered in running order. `before_pass(t)` -> the stream
     inputs (indices) that run right before pass t's first layer."""
     if not 0 <= start <= stop <= n_layers or times < 1:
         raise ValueError(f"a loop over layers {start}..{stop - 1} of {n_layers}, {times} times")

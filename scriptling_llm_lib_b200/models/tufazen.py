@@ -1,8 +1,9 @@
 """Layout of the Tufazen decoder: which parts, with which numbers and tensor names.
 
 The embedding is x = `embed`[token] + `bigram`[r], r a hash of (previous token, token) and the table's last row for a
-sequence's first token. A layer is parallel: with h = norm1(x), x += mixer(h) + ff(h); one norm, of the kind without
-statistics (tanh(alpha v) w + b; tensors `l<i>.norm1`, `.norm1.b`, `.norm1.alpha`), and both sublayers read its output.
+sequence's first token. The two sublayers of a layer work side by side on the same normed stream: h = norm1(x) is formed
+once, by a norm of the kind without statistics (tanh(alpha v) w + b; tensors `l<i>.norm1`, `.norm1.b`, `.norm1.alpha`), and
+x += mixer(h) + ff(h).
 Behind them the layer takes an input from the token itself, x += rms(P (gelu(G x) * e_token)) w (`l<i>.side.gate`,
 `.side.proj`, `.side.norm`; the table `side.embed` is one tensor of which layer i reads its own columns, whichever pass
 it runs in). A run of layers may be gone through several times with the same weights (`loop`): every appearance has a

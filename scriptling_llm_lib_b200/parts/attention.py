@@ -28,9 +28,9 @@ convolution that ran by itself, or the projection. The attention kernels are the
 Four more, again none in the reference. `values_are_keys`: there is no value projection; a position's values are its keys
 as projected, before the rotation (the cache keeps both: the turned keys and the unturned ones as values; the key
 matrix is stacked twice into the one product, so every kernel behind it sees the usual q|k|v row). `softcap`: a score
-s = (q . k) * scale becomes softcap * tanh(s / softcap) before the softmax. `sink_name`: a stored number per head
-whose exponential joins the softmax's denominator; it has no key and no value, is neither scaled nor capped, and
-counts once whatever the number of keys. `gate_per="element"`: the gate matrix is [n_heads * v_dim, hidden] and the
+s = (q . k) * scale becomes softcap * tanh(s / softcap) before the softmax. `sink_name`: a stored logit per head
+that takes part in the softmax's normalisation only: exp(sink) is added to the denominator once, however many keys there
+are and however a step splits them; nothing goes to the numerator, and neither the scale nor the cap touches it. `gate_per="element"`: the gate matrix is [n_heads * v_dim, hidden] and the
 concatenated heads are multiplied element by element with the sigmoid of its product with the mixer's input
 ("head", the default: one logit per head). Capped scores and sinks are known to the attention kernels of the generic set
 (both precisions; scores, cap, softmax and sink float32) and, in bfloat16 with heads of 64 or 128, to the tcgen05 prompt

@@ -83,7 +83,7 @@ CFG_C = config([with_ff(attention(3, 1, 6, 0.6, 2.0, 2, 30.0, RAMP), moe(6, 9, 6
 CFG_D = config([with_ff(attention(4, 2, 64, 0.125, 15.0, 32, 10000.0, RAMP), dense(128, 1.5)),
                 with_ff(latent(4, 32, 16, 32, 64, 64, 0.15, 10000.0), moe(64, 8, 2, 4, 2, 64)),
                 with_ff(attention(2, 1, 128, 0.09, 30.0, 128, 10000.0), moe(32, 4, 3, 1, 1, 32))], width=128, vocab=200, side=16,
-               bigram=(251, 131, 11), loop=(0, 2, 2), logit_scale=0.5)
+               bigram=(251, 131, 11), loop=(0, 2, 2), logit_scale=0.6)
 
 
 def random_weights(cfg, seed, std=0.25):
